@@ -1,0 +1,717 @@
+// B200 (sm_100a) GGUF quantized-linear path: load-time repack / un-repack / dequantise kernels, the
+// activation preparation, the grouped small-batch GEMV/GEMM kernel, the split-K partial sum, and the C ABI
+// declared in include/gq_b200.h.
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <atomic>
+#include "../../include/gq_b200.h"
+#include "gq_decode.cuh"
+#include "_generated/gq_tables.h"
+
+using namespace gq;
+
+// ---------------------------------------------------------------------------------------------------
+// host bookkeeping
+// ---------------------------------------------------------------------------------------------------
+static thread_local char g_cuda_err[256] = "";
+static std::atomic<long long> g_launches{0};
+
+static int cuda_fail(cudaError_t e, const char *what) {
+    snprintf(g_cuda_err, sizeof g_cuda_err, "%s: %s", what, cudaGetErrorString(e));
+    return GQ_ERR_CUDA;
+}
+#define GQ_CUDA(call)                                          \
+    do {                                                       \
+        cudaError_t e_ = (call);                               \
+        if (e_ != cudaSuccess) return cuda_fail(e_, #call);    \
+    } while (0)
+#define GQ_LAUNCHED()                                                    \
+    do {                                                                 \
+        cudaError_t e_ = cudaGetLastError();                             \
+        if (e_ != cudaSuccess) return cuda_fail(e_, "kernel launch");    \
+        g_launches.fetch_add(1, std::memory_order_relaxed);              \
+    } while (0)
+
+extern "C" const char *gq_last_cuda_error(void) { return g_cuda_err; }
+extern "C" int64_t gq_launch_count(void) { return (int64_t)g_launches.load(); }
+extern "C" int gq_bytes_per_256(int type) { return gq_type_bytes(type); }
+
+extern "C" int64_t gq_packed_bytes(int type, int64_t n_out, int64_t K) {
+    const int B = gq_type_bytes(type);
+    if (!B) return GQ_ERR_TYPE;
+    if (n_out < 0 || K <= 0 || K % GQ_QK) return GQ_ERR_SHAPE;
+    return ((n_out + 63) / 64) * (K / GQ_QK) * 64 * (int64_t)B;
+}
+
+extern "C" int gq_slab_map(int type, int32_t *map) {
+    const int B = gq_type_bytes(type);
+    if (!B) return GQ_ERR_TYPE;
+    if (!map) return GQ_ERR_ARG;
+    for (int p = 0; p < 16 * B; ++p) {
+        int row, byte;
+        if (gq_slab_src(type, p, &row, &byte)) return GQ_ERR_TYPE;
+        map[p] = row * B + byte;
+    }
+    return GQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// repack / un-repack: one CTA per (16-row slab, k-block); the slab's raw image goes through shared memory
+// ---------------------------------------------------------------------------------------------------
+#define GQ_MAX_SLAB (16 * 272)
+
+__global__ void __launch_bounds__(256) repack_kernel(int type, int B, const uint8_t *__restrict__ raw, int64_t n_out, int nb,
+                                                     int64_t row_stride, uint8_t *__restrict__ out) {
+    __shared__ __align__(16) uint8_t img[GQ_MAX_SLAB];
+    const int slab = blockIdx.x, kb = blockIdx.y;
+    const int64_t row0 = (int64_t)slab * 16;
+    for (int i = threadIdx.x; i < 16 * B; i += 256) {
+        const int r = i / B, b = i - r * B;
+        img[i] = (row0 + r < n_out) ? raw[(row0 + r) * row_stride + (int64_t)kb * B + b] : (uint8_t)0;
+    }
+    __syncthreads();
+    // packed address: tile = slab / 4, slab-in-tile = slab % 4
+    uint8_t *dst = out + (((int64_t)(slab >> 2) * nb + kb) * 4 + (slab & 3)) * (int64_t)(16 * B);
+    for (int w = threadIdx.x; w < 4 * B; w += 256) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int z = 0; z < 4; ++z) {
+            int row, byte;
+            gq_slab_src(type, 4 * w + z, &row, &byte);
+            v |= (uint32_t)img[row * B + byte] << (8 * z);
+        }
+        reinterpret_cast<uint32_t *>(dst)[w] = v;
+    }
+}
+
+// fills img[16][B] (raw order) from a packed slab
+__device__ __forceinline__ void slab_to_raw_image(int type, int B, const uint8_t *__restrict__ src, uint8_t *img) {
+    for (int w = threadIdx.x; w < 4 * B; w += blockDim.x) {
+        const uint32_t v = reinterpret_cast<const uint32_t *>(src)[w];
+#pragma unroll
+        for (int z = 0; z < 4; ++z) {
+            int row, byte;
+            gq_slab_src(type, 4 * w + z, &row, &byte);
+            img[row * B + byte] = (uint8_t)(v >> (8 * z));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) unrepack_kernel(int type, int B, const uint8_t *__restrict__ tiles, int64_t n_out, int nb,
+                                                       uint8_t *__restrict__ raw, int64_t row_stride) {
+    __shared__ __align__(16) uint8_t img[GQ_MAX_SLAB];
+    const int slab = blockIdx.x, kb = blockIdx.y;
+    const uint8_t *src = tiles + (((int64_t)(slab >> 2) * nb + kb) * 4 + (slab & 3)) * (int64_t)(16 * B);
+    slab_to_raw_image(type, B, src, img);
+    __syncthreads();
+    const int64_t row0 = (int64_t)slab * 16;
+    for (int i = threadIdx.x; i < 16 * B; i += 256) {
+        const int r = i / B, b = i - r * B;
+        if (row0 + r < n_out) raw[(row0 + r) * row_stride + (int64_t)kb * B + b] = img[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// bit-exact dequantiser (fp32 in the format reference's operation order: (d*sc) first, then *q, then -(dmin*m);
+// explicit round-to-nearest multiplies and subtracts so nothing is fused)
+// ---------------------------------------------------------------------------------------------------
+__constant__ uint32_t c_iq3s_grid[512];
+__constant__ int8_t c_iq4_kvalues[16];
+
+__device__ __forceinline__ float h2f(const uint8_t *p) { return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8)))); }
+
+__device__ __forceinline__ void scale_min_k4(const uint8_t *s, int j, int &sc, int &mn) {
+    if (j < 4) { sc = s[j] & 63; mn = s[j + 4] & 63; }
+    else { sc = (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4); mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4); }
+}
+
+// weight w (0..255) of the raw 256-weight segment b
+__device__ float deq_one(int type, const uint8_t *b, int w) {
+    switch (type) {
+        case GQ_Q4_0: { const uint8_t *k = b + 18 * (w >> 5); const int j = w & 31;
+            const int q = (j < 16 ? (k[2 + j] & 0xF) : (k[2 + j - 16] >> 4)) - 8; return __fmul_rn(h2f(k), (float)q); }
+        case GQ_IQ4_NL: { const uint8_t *k = b + 18 * (w >> 5); const int j = w & 31;
+            const int q = c_iq4_kvalues[j < 16 ? (k[2 + j] & 0xF) : (k[2 + j - 16] >> 4)]; return __fmul_rn(h2f(k), (float)q); }
+        case GQ_Q5_0: { const uint8_t *k = b + 22 * (w >> 5); const int j = w & 31;
+            const uint32_t qh = k[2] | (k[3] << 8) | (k[4] << 16) | ((uint32_t)k[5] << 24);
+            const int lo = j < 16 ? (k[6 + j] & 0xF) : (k[6 + j - 16] >> 4);
+            const int q = (lo | (((qh >> j) & 1) << 4)) - 16; return __fmul_rn(h2f(k), (float)q); }
+        case GQ_Q8_0: { const uint8_t *k = b + 34 * (w >> 5); return __fmul_rn((float)(int8_t)k[2 + (w & 31)], h2f(k)); }
+        case GQ_Q2_K: { const int n = w >> 7, t = (w >> 5) & 3, l = w & 31, g = w >> 4;
+            const float dl = __fmul_rn(h2f(b + 80), (float)(b[g] & 0xF)), ml = __fmul_rn(h2f(b + 82), (float)(b[g] >> 4));
+            const int q = (b[16 + 32 * n + l] >> (2 * t)) & 3; return __fsub_rn(__fmul_rn(dl, (float)q), ml); }
+        case GQ_Q3_K: { const int nn = w >> 7, j = (w >> 5) & 3, l = w & 31, i = w >> 4; const uint8_t *s = b + 96;
+            const int lo = (s[i % 8] >> (4 * (i / 8))) & 0xF, hi = (s[8 + i % 4] >> (2 * (i / 4))) & 3;
+            const float dl = __fmul_rn(h2f(b + 108), (float)((lo | (hi << 4)) - 32));
+            const int q = (int)((b[32 + 32 * nn + l] >> (2 * j)) & 3) - (((b[l] >> (4 * nn + j)) & 1) ? 0 : 4);
+            return __fmul_rn(dl, (float)q); }
+        case GQ_Q4_K: { const int ib = w >> 5, p = w & 31; int sc, mn; scale_min_k4(b + 4, ib, sc, mn);
+            const float dl = __fmul_rn(h2f(b), (float)sc), dm = __fmul_rn(h2f(b + 2), (float)mn);
+            const int q = (b[16 + 32 * (ib >> 1) + p] >> (4 * (ib & 1))) & 0xF; return __fsub_rn(__fmul_rn(dl, (float)q), dm); }
+        case GQ_Q5_K: { const int ib = w >> 5, p = w & 31; int sc, mn; scale_min_k4(b + 4, ib, sc, mn);
+            const float dl = __fmul_rn(h2f(b), (float)sc), dm = __fmul_rn(h2f(b + 2), (float)mn);
+            const int q = ((b[48 + 32 * (ib >> 1) + p] >> (4 * (ib & 1))) & 0xF) | (((b[16 + p] >> ib) & 1) << 4);
+            return __fsub_rn(__fmul_rn(dl, (float)q), dm); }
+        case GQ_Q6_K: { const int h = w >> 7, t = (w >> 5) & 3, p = w & 31;
+            const int q = (int)(((b[64 * h + 32 * (t & 1) + p] >> (4 * (t >> 1))) & 0xF) | (((b[128 + 32 * h + p] >> (2 * t)) & 3) << 4)) - 32;
+            const float dl = __fmul_rn(h2f(b + 208), (float)(int8_t)b[192 + (w >> 4)]); return __fmul_rn(dl, (float)q); }
+        case GQ_IQ3_S: { const int ib = w >> 5, j = w & 31, k = j >> 2, e = j & 3;
+            const int s = (b[106 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF; const float db = __fmul_rn(h2f(b), (float)(1 + 2 * s));
+            const int idx = b[2 + 8 * ib + k] | (((b[66 + ib] >> k) & 1) << 8);
+            const float mag = (float)((c_iq3s_grid[idx] >> (8 * e)) & 0xFF);
+            const float v = __fmul_rn(db, mag); return ((b[74 + 4 * ib + (j >> 3)] >> (j & 7)) & 1) ? -v : v; }
+        case GQ_IQ4_XS: { const int ib = w >> 5, j = w & 31; const uint32_t sh = b[2] | (b[3] << 8);
+            const int ls = (int)(((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
+            const float dl = __fmul_rn(h2f(b), (float)ls);
+            const int q = c_iq4_kvalues[j < 16 ? (b[8 + 16 * ib + j] & 0xF) : (b[8 + 16 * ib + j - 16] >> 4)];
+            return __fmul_rn(dl, (float)q); }
+    }
+    return 0.0f;
+}
+
+__global__ void __launch_bounds__(256) dequant_kernel(int type, int B, const uint8_t *__restrict__ tiles, int64_t n_out, int nb,
+                                                      void *__restrict__ out, int out_dtype, int64_t ld) {
+    __shared__ __align__(16) uint8_t img[GQ_MAX_SLAB];
+    const int slab = blockIdx.x, kb = blockIdx.y;
+    const uint8_t *src = tiles + (((int64_t)(slab >> 2) * nb + kb) * 4 + (slab & 3)) * (int64_t)(16 * B);
+    slab_to_raw_image(type, B, src, img);
+    __syncthreads();
+    const int64_t row0 = (int64_t)slab * 16;
+    for (int i = threadIdx.x; i < 16 * 256; i += 256) {
+        const int r = i >> 8, w = i & 255;
+        if (row0 + r >= n_out) continue;
+        const float v = deq_one(type, img + r * B, w);
+        const int64_t o = (row0 + r) * ld + (int64_t)kb * 256 + w;
+        if (out_dtype == 0) reinterpret_cast<float *>(out)[o] = v;
+        else reinterpret_cast<__nv_bfloat16 *>(out)[o] = __float2bfloat16_rn(v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// activation preparation: bf16 row -> fp16 row scaled by a power of two (so any bf16 magnitude fits fp16
+// exactly), the row's inverse scale, and per 16-weight run the fp32 sum split into fp16 hi + lo (the B operand
+// of the minimum-term MMA).  One CTA per batch row.  Plays the role of the reference's quantize_activations_256
+// (gguf-plugin/gluon/tiles_grouped.py:110-139) without quantising: activations keep all their bf16 bits.
+// ---------------------------------------------------------------------------------------------------
+struct Workspace {
+    int *status;
+    float *ex;        // [M]
+    __half *xh;       // [M][K]
+    __half *sx;       // [M][nb][32]: 16 hi then 16 lo
+    float *partials;  // [S][M][n_total]
+};
+
+__host__ __device__ inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+static int64_t ws_layout(int64_t M, int64_t K, int64_t n_total, int split, void *base, Workspace *ws) {
+    int64_t off = 256;
+    const int64_t o_ex = off; off = align256(off + M * 4);
+    const int64_t o_xh = off; off = align256(off + M * K * 2);
+    const int64_t o_sx = off; off = align256(off + M * (K / 16) * 2 * 2);
+    const int64_t o_p = off; if (split > 1) off = align256(off + (int64_t)split * M * n_total * 4);
+    if (ws && base) {
+        uint8_t *b = (uint8_t *)base;
+        ws->status = (int *)b; ws->ex = (float *)(b + o_ex); ws->xh = (__half *)(b + o_xh); ws->sx = (__half *)(b + o_sx);
+        ws->partials = (float *)(b + o_p);
+    }
+    return off;
+}
+
+__global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int K, float *__restrict__ ex,
+                                                     __half *__restrict__ xh, __half *__restrict__ sx, int *status) {
+    __shared__ float red[8];
+    __shared__ float s_scale;
+    const int m = blockIdx.x;
+    if (m == 0 && threadIdx.x == 0) *status = 0;
+    const __nv_bfloat16 *xr = x + (int64_t)m * ldx;
+    const int nrun = K >> 4;
+    float amax = 0.0f;
+    for (int r = threadIdx.x; r < nrun; r += 256) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(xr + 16 * r + j));
+            amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = red[0];
+        for (int i = 1; i < 8; ++i) a = fmaxf(a, red[i]);
+        // scale = 2^(9 - e), amax * scale in [512, 1024); identity for a zero, tiny or non-finite row
+        int e = 9;
+        if (a > 0.0f && a < 3.0e38f) { e = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127; if (e < -100) e = -100; }
+        s_scale = __uint_as_float((uint32_t)(127 + 9 - e) << 23);
+        ex[m] = __uint_as_float((uint32_t)(127 - 9 + e) << 23);
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    __half *xo = xh + (int64_t)m * K;
+    __half *so = sx + (int64_t)m * (K >> 3);
+    for (int r = threadIdx.x; r < nrun; r += 256) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(xr + 16 * r + j));
+            const __half2 h = __floats2half2_rn(v.x * scale, v.y * scale);
+            *reinterpret_cast<__half2 *>(xo + 16 * r + j) = h;
+            sum += __low2float(h) + __high2float(h);
+        }
+        const __half hi = __float2half_rn(sum);
+        const __half lo = __float2half_rn(sum - __half2float(hi));
+        const int kb = r >> 4, rr = r & 15;
+        so[kb * 32 + rr] = hi;
+        so[kb * 32 + 16 + rr] = lo;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// grouped small-batch kernel.  One CTA per descriptor row (64 output columns of one shard x a k-range):
+// a producer warp streams the tile's k-blocks (one bulk copy each) plus the matching activation rows through
+// an mbarrier ring; four consumer warps each own a 16-row slab, dequantise it in registers and run m16n8k16
+// MMAs with the weights on the M side and the batch rows on the N side (8 batch rows per MMA, MT MMAs deep).
+// Replaces tiles_grouped_kernel / _run (gguf-plugin/gluon/tiles_grouped.py:343-1201).
+// ---------------------------------------------------------------------------------------------------
+#define GQ_XROW_BYTES 544   // 256 fp16 + 32 bytes of padding: the eight batch rows of an MMA hit distinct banks
+#define GQ_SXROW_BYTES 64
+#define GQ_CONSUMER_WARPS 4
+
+struct GemvParams {
+    const uint8_t *packed;
+    const int32_t *desc;
+    const __half *xh;
+    const __half *sx;
+    const float *ex;
+    __nv_bfloat16 *y;
+    float *partials;
+    int *status;
+    int M, K, nb, split, stages;
+    int64_t ldy, n_total;
+    int wbytes_max;      // largest tile bytes in the launch (stage stride of the weight buffers)
+    int has_iq3s;
+};
+
+template <int TYPE, int MT, int P>
+struct PairStep {
+    __device__ __forceinline__ static void run(const Dec<TYPE> &dec, const uint8_t *xs, int g, int t, float (&blk)[MT][4]) {
+        uint32_t a[2][4];
+        dec.template pair<P>(a);
+        const uint8_t *xb = xs + g * GQ_XROW_BYTES + 8 * t + 64 * P;   // run 2P at halves 32P + 4t
+        if constexpr (Dec<TYPE>::GROUP == 32) {
+            float s0, s1;
+            dec.template scale<P>(s0, s1);
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt) {
+                float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint2 b0 = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES);
+                const uint2 b1 = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES + 32);
+                mma16816(tmp, a[0], b0.x, b0.y);
+                mma16816(tmp, a[1], b1.x, b1.y);
+                blk[nt][0] = fmaf(s0, tmp[0], blk[nt][0]);
+                blk[nt][1] = fmaf(s0, tmp[1], blk[nt][1]);
+                blk[nt][2] = fmaf(s1, tmp[2], blk[nt][2]);
+                blk[nt][3] = fmaf(s1, tmp[3], blk[nt][3]);
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                float s0, s1;
+                if (u == 0) dec.template scale<2 * P>(s0, s1); else dec.template scale<2 * P + 1>(s0, s1);
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt) {
+                    float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint2 b = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES + 32 * u);
+                    mma16816(tmp, a[u], b.x, b.y);
+                    blk[nt][0] = fmaf(s0, tmp[0], blk[nt][0]);
+                    blk[nt][1] = fmaf(s0, tmp[1], blk[nt][1]);
+                    blk[nt][2] = fmaf(s1, tmp[2], blk[nt][2]);
+                    blk[nt][3] = fmaf(s1, tmp[3], blk[nt][3]);
+                }
+            }
+        }
+        if constexpr (P < 7) PairStep<TYPE, MT, P + 1>::run(dec, xs, g, t, blk);
+    }
+};
+
+// one k-block of one slab: acc += d * sum_groups(scale * (W_int . x)) - dmin * (mins . run sums)
+template <int TYPE, int MT>
+__device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *xs, const uint8_t *sxs, const DecAux &aux, int lane,
+                                            float (&acc)[MT][4]) {
+    Dec<TYPE> dec;
+    dec.load(slab, lane, aux);
+    const int g = lane >> 2, t = lane & 3;
+    float blk[MT][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) blk[nt][0] = blk[nt][1] = blk[nt][2] = blk[nt][3] = 0.f;
+    PairStep<TYPE, MT, 0>::run(dec, xs, g, t, blk);
+    float d0, d1;
+    dec.kscale(d0, d1);
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+        acc[nt][0] = fmaf(d0, blk[nt][0], acc[nt][0]);
+        acc[nt][1] = fmaf(d0, blk[nt][1], acc[nt][1]);
+        acc[nt][2] = fmaf(d1, blk[nt][2], acc[nt][2]);
+        acc[nt][3] = fmaf(d1, blk[nt][3], acc[nt][3]);
+    }
+    if constexpr (Dec<TYPE>::HAS_MIN) {
+        uint32_t am[4];
+        dec.min_frag(am);
+        float m0, m1;
+        dec.min_scale(m0, m1);
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) {
+            float mm[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint8_t *sb = sxs + (nt * 8 + g) * GQ_SXROW_BYTES + 8 * t;
+            const uint2 bh = *reinterpret_cast<const uint2 *>(sb);
+            const uint2 bl = *reinterpret_cast<const uint2 *>(sb + 32);
+            mma16816(mm, am, bh.x, bh.y);
+            mma16816(mm, am, bl.x, bl.y);
+            acc[nt][0] = fmaf(-m0, mm[0], acc[nt][0]);
+            acc[nt][1] = fmaf(-m0, mm[1], acc[nt][1]);
+            acc[nt][2] = fmaf(-m1, mm[2], acc[nt][2]);
+            acc[nt][3] = fmaf(-m1, mm[3], acc[nt][3]);
+        }
+    }
+}
+
+template <int MT>
+__device__ __forceinline__ void slab_kblock_any(int type, const uint8_t *slab, const uint8_t *xs, const uint8_t *sxs, const DecAux &aux,
+                                                int lane, float (&acc)[MT][4]) {
+    switch (type) {
+        case GQ_Q4_0: slab_kblock<GQ_Q4_0, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_Q5_0: slab_kblock<GQ_Q5_0, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_Q8_0: slab_kblock<GQ_Q8_0, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_Q2_K: slab_kblock<GQ_Q2_K, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_Q3_K: slab_kblock<GQ_Q3_K, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_Q4_K: slab_kblock<GQ_Q4_K, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_Q5_K: slab_kblock<GQ_Q5_K, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_Q6_K: slab_kblock<GQ_Q6_K, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_IQ4_NL: slab_kblock<GQ_IQ4_NL, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_IQ3_S: slab_kblock<GQ_IQ3_S, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_IQ4_XS: slab_kblock<GQ_IQ4_XS, MT>(slab, xs, sxs, aux, lane, acc); break;
+    }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // layout: [stages x (weights wbytes_max | x tile | sx tile)] [full barriers] [empty barriers] [IQ3_S grid]
+    const int xbytes = 8 * MT * GQ_XROW_BYTES, sxbytes = 8 * MT * GQ_SXROW_BYTES;
+    const int stage_bytes = p.wbytes_max + xbytes + sxbytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)p.stages * stage_bytes);
+    uint64_t *empty = full + p.stages;
+    uint2 *grid_s = reinterpret_cast<uint2 *>(empty + p.stages);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int32_t *d = p.desc + (int64_t)blockIdx.x * GQ_DESC_WORDS;
+    const int64_t off = (int64_t)d[0] * 16;
+    const int type = d[1], col0 = d[2], nvalid = d[3], kb0 = d[4], kb1 = d[5], split_idx = d[6];
+    const int B = gq_type_bytes(type);
+    const int tile_bytes = 64 * B;
+    const int nk = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, GQ_CONSUMER_WARPS); }
+        fence_barrier_init();
+    }
+    if (p.has_iq3s && type == GQ_IQ3_S) {
+        for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+            const uint32_t w = c_iq3s_grid[i];
+            uint2 e;
+            e.x = h2_as_u32(__floats2half2_rn((float)(w & 0xFF), (float)((w >> 8) & 0xFF)));
+            e.y = h2_as_u32(__floats2half2_rn((float)((w >> 16) & 0xFF), (float)(w >> 24)));
+            grid_s[i] = e;
+        }
+    }
+    __syncthreads();
+
+    if (warp == GQ_CONSUMER_WARPS) {
+        // ---- producer ----
+        const uint8_t *src = p.packed + off + (int64_t)kb0 * tile_bytes;
+        const uint32_t tx = (uint32_t)tile_bytes + (uint32_t)p.M * (512u + GQ_SXROW_BYTES);
+        for (int i = 0; i < nk; ++i) {
+            const int s = i % p.stages;
+            if (i >= p.stages) {
+                if (!mbar_wait(empty + s, ((i / p.stages) - 1) & 1)) { if (lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT); break; }
+            }
+            uint8_t *st = smem + (size_t)s * stage_bytes;
+            if (lane == 0) {
+                mbar_expect_tx(full + s, tx);
+                bulk_g2s(st, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + s);
+            }
+            __syncwarp();
+            const int kb = kb0 + i;
+            for (int n = lane; n < p.M; n += 32) {
+                bulk_g2s(st + p.wbytes_max + n * GQ_XROW_BYTES, p.xh + (int64_t)n * p.K + (int64_t)kb * 256, 512u, full + s);
+                bulk_g2s(st + p.wbytes_max + xbytes + n * GQ_SXROW_BYTES, p.sx + ((int64_t)n * p.nb + kb) * 32, GQ_SXROW_BYTES, full + s);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ----
+    DecAux aux;
+    aux.iq3s_grid = grid_s;
+    {
+        uint32_t tb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            tb[j] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tb[j] |= (uint32_t)(uint8_t)(c_iq4_kvalues[4 * j + i] + 128) << (8 * i);
+        }
+        aux.iq4 = {tb[0], tb[1], tb[2], tb[3]};
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+
+    bool ok = true;
+    for (int i = 0; i < nk; ++i) {
+        const int s = i % p.stages;
+        if (!mbar_wait(full + s, (i / p.stages) & 1)) { ok = false; break; }
+        const uint8_t *st = smem + (size_t)s * stage_bytes;
+        slab_kblock_any<MT>(type, st + warp * 16 * B, st + p.wbytes_max, st + p.wbytes_max + xbytes, aux, lane, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+    }
+    if (!ok) { if (lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT); return; }
+
+    // ---- epilogue: rows of the MMA are output columns, columns of the MMA are batch rows ----
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = warp * 16 + g + 8 * (j >> 1);      // row inside the 64-row tile
+            const int n = nt * 8 + 2 * t + (j & 1);          // batch row
+            if (r < nvalid && n < p.M) {
+                const float v = acc[nt][j] * p.ex[n];
+                if (p.split == 1) p.y[(int64_t)n * p.ldy + col0 + r] = __float2bfloat16_rn(v);
+                else p.partials[((int64_t)split_idx * p.M + n) * p.n_total + col0 + r] = v;
+            }
+        }
+}
+
+// Y = sum over splits of the fp32 partials, rounded once to bf16 (reference: sum_partials,
+// gguf-plugin/gluon/tiles_grouped.py:142-162)
+__global__ void __launch_bounds__(256) sum_partials_kernel(const float *__restrict__ P, int S, int64_t M, int64_t n_total,
+                                                           __nv_bfloat16 *__restrict__ y, int64_t ldy) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= M * n_total) return;
+    float a = 0.f;
+    for (int s = 0; s < S; ++s) a += P[(int64_t)s * M * n_total + i];
+    const int64_t m = i / n_total, c = i - m * n_total;
+    y[m * ldy + c] = __float2bfloat16_rn(a);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------------
+static int ensure_tables() {
+    // per-device one-time upload of the two format tables into constant memory
+    static std::atomic<unsigned long long> done_mask{0};
+    int dev = 0;
+    GQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && (done_mask.load() >> dev) & 1ull) return GQ_OK;
+    GQ_CUDA(cudaMemcpyToSymbol(c_iq3s_grid, GQ_IQ3S_GRID, sizeof GQ_IQ3S_GRID));
+    GQ_CUDA(cudaMemcpyToSymbol(c_iq4_kvalues, GQ_IQ4_KVALUES, sizeof GQ_IQ4_KVALUES));
+    if (dev < 64) done_mask.fetch_or(1ull << dev);
+    return GQ_OK;
+}
+
+static int check_tensor_args(int type, int64_t n_out, int64_t K) {
+    if (!gq_type_bytes(type)) return GQ_ERR_TYPE;
+    if (n_out < 0 || K <= 0 || K % GQ_QK || K / GQ_QK > 65535) return GQ_ERR_SHAPE;
+    return GQ_OK;
+}
+
+extern "C" int gq_repack(int type, const void *raw_dev, int64_t n_out, int64_t K, int64_t raw_row_stride, void *out_dev, void *stream) {
+    if (int rc = check_tensor_args(type, n_out, K)) return rc;
+    const int B = gq_type_bytes(type);
+    const int nb = (int)(K / GQ_QK);
+    if (n_out == 0) return GQ_OK;
+    if (!raw_dev || !out_dev || ((uintptr_t)out_dev & 15) || raw_row_stride < (int64_t)nb * B) return GQ_ERR_ARG;
+    const int64_t slabs = ((n_out + 63) / 64) * 4;
+    if (slabs > 0x7fffffff) return GQ_ERR_LIMIT;
+    repack_kernel<<<dim3((unsigned)slabs, (unsigned)nb), 256, 0, (cudaStream_t)stream>>>(type, B, (const uint8_t *)raw_dev, n_out, nb,
+                                                                                     raw_row_stride, (uint8_t *)out_dev);
+    GQ_LAUNCHED();
+    return GQ_OK;
+}
+
+extern "C" int gq_unrepack(int type, const void *tiles_dev, int64_t n_out, int64_t K, void *raw_dev, int64_t raw_row_stride, void *stream) {
+    if (int rc = check_tensor_args(type, n_out, K)) return rc;
+    const int B = gq_type_bytes(type);
+    const int nb = (int)(K / GQ_QK);
+    if (n_out == 0) return GQ_OK;
+    if (!raw_dev || !tiles_dev || ((uintptr_t)tiles_dev & 15) || raw_row_stride < (int64_t)nb * B) return GQ_ERR_ARG;
+    const int64_t slabs = ((n_out + 63) / 64) * 4;
+    if (slabs > 0x7fffffff) return GQ_ERR_LIMIT;
+    unrepack_kernel<<<dim3((unsigned)slabs, (unsigned)nb), 256, 0, (cudaStream_t)stream>>>(type, B, (const uint8_t *)tiles_dev, n_out, nb,
+                                                                                       (uint8_t *)raw_dev, raw_row_stride);
+    GQ_LAUNCHED();
+    return GQ_OK;
+}
+
+extern "C" int gq_dequant(int type, const void *tiles_dev, int64_t n_out, int64_t K, void *out_dev, int out_dtype, int64_t ld, void *stream) {
+    if (int rc = check_tensor_args(type, n_out, K)) return rc;
+    const int B = gq_type_bytes(type);
+    const int nb = (int)(K / GQ_QK);
+    if (n_out == 0) return GQ_OK;
+    if (!out_dev || !tiles_dev || ((uintptr_t)tiles_dev & 15) || ld < K || (out_dtype != 0 && out_dtype != 1)) return GQ_ERR_ARG;
+    if (int rc = ensure_tables()) return rc;
+    const int64_t slabs = ((n_out + 63) / 64) * 4;
+    if (slabs > 0x7fffffff) return GQ_ERR_LIMIT;
+    dequant_kernel<<<dim3((unsigned)slabs, (unsigned)nb), 256, 0, (cudaStream_t)stream>>>(type, B, (const uint8_t *)tiles_dev, n_out, nb, out_dev,
+                                                                                      out_dtype, ld);
+    GQ_LAUNCHED();
+    return GQ_OK;
+}
+
+extern "C" int64_t gq_desc_rows(int n_shards, const int64_t *n_outs, int split) {
+    if (n_shards <= 0 || !n_outs || split < 1) return GQ_ERR_ARG;
+    int64_t tiles = 0;
+    for (int i = 0; i < n_shards; ++i) { if (n_outs[i] < 0) return GQ_ERR_SHAPE; tiles += (n_outs[i] + 63) / 64; }
+    return tiles * split;
+}
+
+extern "C" int64_t gq_build_descs(int n_shards, const int32_t *types, const int64_t *n_outs, int64_t K, int split, int32_t *desc_host) {
+    if (n_shards <= 0 || !types || !n_outs || !desc_host) return GQ_ERR_ARG;
+    if (K <= 0 || K % GQ_QK) return GQ_ERR_SHAPE;
+    const int64_t nb = K / GQ_QK;
+    if (split < 1 || split > nb) return GQ_ERR_ARG;
+    int64_t base = 0, col0 = 0, row = 0;
+    for (int i = 0; i < n_shards; ++i) {
+        const int B = gq_type_bytes(types[i]);
+        if (!B) return GQ_ERR_TYPE;
+        if (n_outs[i] < 0) return GQ_ERR_SHAPE;
+        const int64_t n_tiles = (n_outs[i] + 63) / 64, tile_kb_bytes = 64 * (int64_t)B;
+        for (int64_t ti = 0; ti < n_tiles; ++ti)
+            for (int s = 0; s < split; ++s) {
+                const int64_t o = base + ti * nb * tile_kb_bytes;
+                if ((o >> 4) > 0x7fffffff || col0 + ti * 64 > 0x7fffffff) return GQ_ERR_LIMIT;
+                int32_t *r = desc_host + row * GQ_DESC_WORDS;
+                r[0] = (int32_t)(o >> 4);
+                r[1] = types[i];
+                r[2] = (int32_t)(col0 + ti * 64);
+                r[3] = (int32_t)(n_outs[i] - ti * 64 < 64 ? n_outs[i] - ti * 64 : 64);
+                r[4] = (int32_t)((s * nb) / split);
+                r[5] = (int32_t)(((s + 1) * nb) / split);
+                r[6] = s;
+                r[7] = 0;
+                ++row;
+            }
+        base += n_tiles * nb * tile_kb_bytes;
+        col0 += n_outs[i];
+    }
+    return row;
+}
+
+extern "C" int gq_split_for(int64_t n_tiles, int64_t nb, int64_t M, int avg_bytes_per_256, int sm_count) {
+    if (n_tiles <= 0 || nb <= 0) return 1;
+    if (sm_count <= 0) sm_count = 148;
+    // enough CTAs for about three per SM, each keeping at least two k-blocks, the fp32 partials held to a
+    // sixth of the weight bytes
+    int64_t s = (3 * (int64_t)sm_count + n_tiles - 1) / n_tiles;
+    if (s > nb / 2) s = nb / 2;
+    if (s > 16) s = 16;
+    if (M > 0 && avg_bytes_per_256 > 0) {
+        // partial traffic 2 * S * M * 64 * 4 bytes per tile against nb * 64 * bytes_per_256 of weights
+        const int64_t cap = (nb * avg_bytes_per_256) / (6 * 8 * (M < 8 ? 8 : M));
+        if (s > cap) s = cap;
+    }
+    if (s < 1) s = 1;
+    if (s > nb) s = nb;
+    return (int)s;
+}
+
+extern "C" int64_t gq_workspace_bytes(int64_t M, int64_t K, int64_t n_total, int split) {
+    if (M < 0 || K <= 0 || K % GQ_QK || n_total < 0 || split < 1) return GQ_ERR_SHAPE;
+    return ws_layout(M, K, n_total, split, nullptr, nullptr);
+}
+
+template <int MT>
+static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream) {
+    const int xbytes = 8 * MT * GQ_XROW_BYTES, sxbytes = 8 * MT * GQ_SXROW_BYTES;
+    const int stage_bytes = p.wbytes_max + xbytes + sxbytes;
+    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? 4096 : 0);
+    // opt in once per device to the largest dynamic shared memory any launch of this variant can ask for
+    static std::atomic<unsigned long long> done_mask{0};
+    int dev = 0;
+    GQ_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
+        const int max_smem = 4 * (64 * 272 + xbytes + sxbytes) + 4 * 16 + 4096;
+        GQ_CUDA(cudaFuncSetAttribute(gemv_grouped_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem > 232448 ? 232448 : max_smem));
+        if (dev < 64) done_mask.fetch_or(1ull << dev);
+    }
+    if (smem > 232448) return GQ_ERR_LIMIT;
+    gemv_grouped_kernel<MT><<<(unsigned)n_desc, 32 * (GQ_CONSUMER_WARPS + 1), smem, stream>>>(p);
+    GQ_LAUNCHED();
+    return GQ_OK;
+}
+
+extern "C" int gq_run_info(int n_shards, const int32_t *types) {
+    if (n_shards <= 0 || !types) return GQ_ERR_ARG;
+    int maxb = 0, iq3s = 0;
+    for (int i = 0; i < n_shards; ++i) {
+        const int B = gq_type_bytes(types[i]);
+        if (!B) return GQ_ERR_TYPE;
+        if (B > maxb) maxb = B;
+        if (types[i] == GQ_IQ3_S) iq3s = 1;
+    }
+    return maxb | (iq3s << 16);
+}
+
+extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                               int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
+                               int64_t workspace_bytes, void *stream) {
+    if (M < 0 || M > GQ_MAX_GEMV_ROWS || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0 || split < 1) return GQ_ERR_SHAPE;
+    if (M == 0 || n_total == 0 || n_desc == 0) return GQ_OK;
+    if (!x_dev || !packed_dev || !desc_dev || !y_dev || !workspace_dev) return GQ_ERR_ARG;
+    if (((uintptr_t)packed_dev & 15) || ((uintptr_t)workspace_dev & 255) || ((uintptr_t)x_dev & 3) || ldx < K || ldy < n_total) return GQ_ERR_ARG;
+    if (n_desc > 0x7fffffff) return GQ_ERR_LIMIT;
+    Workspace ws;
+    const int64_t need = ws_layout(M, K, n_total, split, workspace_dev, &ws);
+    if (workspace_bytes < need) return GQ_ERR_WORKSPACE;
+    if (int rc = ensure_tables()) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    prep_x_kernel<<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16 *)x_dev, ldx, (int)K, ws.ex, ws.xh, ws.sx, ws.status);
+    GQ_LAUNCHED();
+
+    GemvParams p;
+    p.packed = (const uint8_t *)packed_dev; p.desc = desc_dev; p.xh = ws.xh; p.sx = ws.sx; p.ex = ws.ex;
+    p.y = (__nv_bfloat16 *)y_dev; p.partials = ws.partials; p.status = ws.status;
+    p.M = (int)M; p.K = (int)K; p.nb = (int)(K / GQ_QK); p.split = split; p.ldy = ldy; p.n_total = n_total;
+    const int maxb = run_info & 0xFFFF;
+    if (maxb < 84 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
+    p.wbytes_max = 64 * maxb;   // every stage can hold a tile of any shard of the run
+    p.has_iq3s = (run_info >> 16) & 1;
+    const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
+    p.stages = mt == 1 ? 4 : mt == 2 ? 4 : mt == 4 ? 3 : 3;
+    int rc;
+    switch (mt) {
+        case 1: rc = launch_gemv<1>(p, n_desc, st); break;
+        case 2: rc = launch_gemv<2>(p, n_desc, st); break;
+        case 4: rc = launch_gemv<4>(p, n_desc, st); break;
+        default: rc = launch_gemv<8>(p, n_desc, st); break;
+    }
+    if (rc) return rc;
+    if (split > 1) {
+        const int64_t n = M * n_total;
+        sum_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws.partials, split, M, n_total, (__nv_bfloat16 *)y_dev, ldy);
+        GQ_LAUNCHED();
+    }
+    return GQ_OK;
+}
+
+extern "C" int gq_read_status(const void *workspace_dev, int64_t workspace_bytes, void *stream) {
+    if (!workspace_dev || workspace_bytes < 256) return GQ_ERR_ARG;
+    int v = 0;
+    GQ_CUDA(cudaMemcpyAsync(&v, workspace_dev, sizeof v, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    GQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return v;
+}

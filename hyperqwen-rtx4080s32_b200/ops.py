@@ -1,0 +1,224 @@
+"""Operator layer over the C ABI: the functions the GGUF LinearMethod calls, with the reference's names
+and argument meaning (gguf-plugin/gluon/interface.py, gguf-plugin/gluon/tiles.py,
+gguf-plugin/gluon/tiles_grouped.py), and the torch custom op that wraps the per-call one so a compiled
+graph sees a single traceable call (gguf-plugin/patches/gguf-tiles-grouped.patch:28-74).
+
+All compute happens in libgq_b200.so on the current CUDA device and stream; tensors only carry device
+memory.  There is no fallback: a missing library or a CPU tensor raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from . import formats as F
+from ._lib import DESC_WORDS, MAX_GEMV_ROWS, GqError, check, lib
+
+TILE_TYPES = F.SUPPORTED_TYPES   # every one of the eleven types is held tile-major (the reference: GLUON_TILE_TYPES)
+GEMV_MAX_ROWS = MAX_GEMV_ROWS    # row-count dispatch threshold: above it the prefill kernel takes over
+
+
+def _stream_ptr(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise GqError(f"{what} must be a CUDA tensor (there is no CPU path)")
+
+
+def _i32_array(vals: Sequence[int]):
+    return (ctypes.c_int32 * len(vals))(*[int(v) for v in vals])
+
+
+def _i64_array(vals: Sequence[int]):
+    return (ctypes.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+def sm_count(device=None) -> int:
+    if torch.cuda.is_available():
+        return torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
+    return 148
+
+
+# ---- host-only helpers (usable without a GPU) -----------------------------------------------------
+
+def slab_map(wtype: int) -> np.ndarray:
+    """map[p] = row * bytes_per_256 + byte: the raw source of packed byte p of a 16-row slab."""
+    bb = lib().gq_bytes_per_256(int(wtype))
+    if bb == 0:
+        raise GqError(f"unsupported GGML type {wtype}")
+    m = np.empty(16 * bb, dtype=np.int32)
+    check(lib().gq_slab_map(int(wtype), m.ctypes.data_as(ctypes.c_void_p)), "gq_slab_map")
+    return m
+
+
+def packed_bytes(wtype: int, n_out: int, k: int) -> int:
+    return check(lib().gq_packed_bytes(int(wtype), int(n_out), int(k)), "gq_packed_bytes")
+
+
+def build_descs(wtypes: Sequence[int], n_outs: Sequence[int], k: int, split: int) -> np.ndarray:
+    """The descriptor table int32 [n_tiles * split, 8] of a run of shards (host array)."""
+    n = len(wtypes)
+    no = _i64_array(n_outs)
+    rows = check(lib().gq_desc_rows(n, no, int(split)), "gq_desc_rows")
+    out = np.zeros((rows, DESC_WORDS), dtype=np.int32)
+    got = check(lib().gq_build_descs(n, _i32_array(wtypes), no, int(k), int(split), out.ctypes.data_as(ctypes.c_void_p)),
+                "gq_build_descs")
+    assert got == rows
+    return out
+
+
+def grouped_split_for(n_tiles: int, nb: int, m: int | None = None, block_bytes: int | None = None, sms: int | None = None) -> int:
+    """Split-K of a grouped launch (reference: grouped_split_for, gguf-plugin/gluon/tiles_grouped.py:237-250)."""
+    return int(lib().gq_split_for(int(n_tiles), int(nb), int(m or 0), int(block_bytes or 0), int(sms or sm_count())))
+
+
+def run_info(wtypes: Sequence[int]) -> int:
+    return check(lib().gq_run_info(len(wtypes), _i32_array(wtypes)), "gq_run_info")
+
+
+# ---- load time -----------------------------------------------------------------------------------
+
+def repack_tiles(raw: torch.Tensor, n_out: int, wtype: int) -> torch.Tensor:
+    """raw uint8 [n_out, nb * bytes_per_256] (any row stride) -> tiles uint8 [ceil(n_out/64), nb, 64 * bytes_per_256]."""
+    _need_cuda(raw, "raw")
+    if raw.dtype != torch.uint8 or raw.dim() != 2 or raw.shape[0] != n_out:
+        raise GqError(f"raw must be uint8 [n_out, row_bytes], got {raw.dtype} {tuple(raw.shape)}")
+    bb = F.BYTES_PER_256[int(wtype)]
+    if raw.shape[1] % bb or raw.stride(1) != 1:
+        raise GqError(f"row bytes {raw.shape[1]} are not whole {bb}-byte k-blocks of type {wtype}")
+    nb = raw.shape[1] // bb
+    n_tiles = -(-n_out // 64)
+    out = torch.empty((n_tiles, nb, 64 * bb), dtype=torch.uint8, device=raw.device)
+    with torch.cuda.device(raw.device):
+        check(lib().gq_repack(int(wtype), raw.data_ptr(), n_out, nb * 256, raw.stride(0), out.data_ptr(), _stream_ptr(raw)), "gq_repack")
+    return out
+
+
+def unrepack_tiles(tiles: torch.Tensor, n_out: int, wtype: int) -> torch.Tensor:
+    """tiles -> the raw rows uint8 [n_out, nb * bytes_per_256], bit for bit."""
+    _need_cuda(tiles, "tiles")
+    bb = F.BYTES_PER_256[int(wtype)]
+    if tiles.dtype != torch.uint8 or tiles.dim() != 3 or tiles.shape[2] != 64 * bb or not tiles.is_contiguous():
+        raise GqError(f"tiles must be contiguous uint8 [n_tiles, nb, {64 * bb}], got {tuple(tiles.shape)}")
+    nb = tiles.shape[1]
+    raw = torch.empty((n_out, nb * bb), dtype=torch.uint8, device=tiles.device)
+    with torch.cuda.device(tiles.device):
+        check(lib().gq_unrepack(int(wtype), tiles.data_ptr(), n_out, nb * 256, raw.data_ptr(), raw.stride(0), _stream_ptr(tiles)), "gq_unrepack")
+    return raw
+
+
+def dequantize_tiles(tiles: torch.Tensor, n_out: int, k: int, wtype: int, dtype=torch.float32) -> torch.Tensor:
+    """tiles -> weights [n_out, k]: fp32 bit-identical to gguf.quants.dequantize, or bf16 (that value rounded)."""
+    _need_cuda(tiles, "tiles")
+    if dtype not in (torch.float32, torch.bfloat16):
+        raise GqError("dequantize_tiles produces float32 or bfloat16")
+    out = torch.empty((n_out, k), dtype=dtype, device=tiles.device)
+    with torch.cuda.device(tiles.device):
+        check(lib().gq_dequant(int(wtype), tiles.data_ptr(), n_out, k, out.data_ptr(), 0 if dtype == torch.float32 else 1, k,
+                               _stream_ptr(tiles)), "gq_dequant")
+    return out
+
+
+def pack_tiles(shards: Sequence[tuple[torch.Tensor, int, int]]):
+    """[(tiles, n_out, type)] -> (packed uint8 buffer, meta): the shards' tiles back to back in one buffer."""
+    nb = None
+    for t, n_out, wt in shards:
+        if t.shape[0] != -(-n_out // 64) or (nb is not None and t.shape[1] != nb):
+            raise GqError("shards of a run must share K and hold ceil(n_out/64) tiles")
+        nb = int(t.shape[1])
+    packed = torch.cat([t.reshape(-1) for t, _, _ in shards])
+    meta = {"nb": nb, "n_outs": [int(n) for _, n, _ in shards], "types": [int(w) for _, _, w in shards],
+            "n_total": sum(int(n) for _, n, _ in shards)}
+    return packed, meta
+
+
+def prepare_grouped_layer(tiles_list: Sequence[torch.Tensor], n_outs: Sequence[int], wtypes: Sequence[int], ms=range(1, GEMV_MAX_ROWS + 1)):
+    """The loader's step for a run of shards (reference: prepare_grouped_layer,
+    gguf-plugin/gluon/tiles_grouped.py:253-267): (packed buffer, the shards' tiles as views into it, the
+    descriptor tables of every split a batch of 1..64 rows can choose plus split 1, those splits, nb, the
+    run's average bytes per 256 weights)."""
+    packed, meta = pack_tiles(list(zip(tiles_list, n_outs, wtypes)))
+    views, off = [], 0
+    for t in tiles_list:
+        views.append(packed[off:off + t.numel()].view(t.shape))
+        off += t.numel()
+    nb, n_total = meta["nb"], meta["n_total"]
+    n_tiles = sum(-(-int(n) // 64) for n in n_outs)
+    block_bytes = int(round(sum(int(n) * F.BYTES_PER_256[int(w)] for n, w in zip(n_outs, wtypes)) / max(1, n_total)))
+    sms = sm_count(packed.device)
+    splits = sorted({grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=sms) for m in ms} | {1})
+    descs = [torch.from_numpy(build_descs(wtypes, n_outs, nb * 256, s)).to(packed.device) for s in splits]
+    return packed, views, descs, splits, nb, block_bytes
+
+
+# ---- per call ------------------------------------------------------------------------------------
+
+def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, split: int, wtypes: Sequence[int], n_total: int,
+                 out: torch.Tensor | None = None) -> torch.Tensor:
+    """One grouped launch for 1..64 rows: x bf16 [M, K] -> out bf16 [M, n_total] (out may be a column view)."""
+    _need_cuda(x, "x")
+    if x.dtype != torch.bfloat16 or x.dim() != 2:
+        raise GqError(f"x must be bf16 [M, K], got {x.dtype} {tuple(x.shape)}")
+    m, k = int(x.shape[0]), int(x.shape[1])
+    if m > GEMV_MAX_ROWS:
+        raise GqError(f"grouped_gemm takes at most {GEMV_MAX_ROWS} rows, got {m}")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty((m, n_total), dtype=torch.bfloat16, device=x.device)
+    elif out.dtype != torch.bfloat16 or out.shape != (m, n_total) or (m > 0 and out.stride(1) != 1):
+        raise GqError("out must be bf16 [M, n_total] with unit column stride")
+    if m == 0 or n_total == 0:
+        return out
+    L = lib()
+    ws_bytes = check(L.gq_workspace_bytes(m, k, n_total, int(split)), "gq_workspace_bytes")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(L.gq_gemv_grouped(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc.data_ptr(), int(desc.shape[0]), int(split),
+                                run_info(wtypes), out.data_ptr(), out.stride(0), n_total, ws.data_ptr(), ws_bytes, _stream_ptr(x)),
+              "gq_gemv_grouped")
+    return out
+
+
+def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[torch.Tensor], desc_splits: list[int],
+                          tiles: list[torch.Tensor], n_outs: list[int], weight_types: list[int], nb: int, block_bytes: int) -> torch.Tensor:
+    """A layer's run of shards in one call: x bf16 [M, K] -> [M, sum(n_outs)] (reference:
+    gluon_mul_mat_tiles_grouped, gguf-plugin/gluon/interface.py:141-188).  The row-count dispatch lives
+    here, inside the op: up to 64 rows one grouped launch at the split of the table for that row count;
+    above, 64-row blocks of the same kernel at split 1 (the weights stream once per block)."""
+    m = int(x.shape[0])
+    n_total = sum(int(n) for n in n_outs)
+    out = torch.empty((m, n_total), dtype=x.dtype, device=x.device)
+    if m == 0:
+        return out
+    n_tiles = sum(-(-int(n) // 64) for n in n_outs)
+    if m <= GEMV_MAX_ROWS:
+        s = grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=sm_count(x.device))
+        if s not in desc_splits:
+            s = 1
+        grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, out=out)
+        return out
+    d1 = descs[desc_splits.index(1)]
+    for r0 in range(0, m, GEMV_MAX_ROWS):
+        r1 = min(m, r0 + GEMV_MAX_ROWS)
+        grouped_gemm(x[r0:r1], packed, d1, 1, weight_types, n_total, out=out[r0:r1])
+    return out
+
+
+# ---- torch custom op (traceable boundary) ----------------------------------------------------------
+
+def _fake(x, packed, descs, desc_splits, tiles, n_outs, weight_types, nb, block_bytes):
+    return torch.empty(x.shape[0], sum(n_outs), dtype=x.dtype, device=x.device)
+
+
+_OP_LIB = torch.library.Library("gq_b200", "FRAGMENT")
+_OP_LIB.define("fused_mul_mat_gguf_tiles_grouped(Tensor x, Tensor packed, Tensor[] descs, int[] desc_splits, Tensor[] tiles, "
+               "int[] n_outs, int[] weight_types, int nb, int block_bytes) -> Tensor")
+_OP_LIB.impl("fused_mul_mat_gguf_tiles_grouped", mul_mat_tiles_grouped, "CUDA")
+torch.library.register_fake("gq_b200::fused_mul_mat_gguf_tiles_grouped")(_fake)
+fused_mul_mat_gguf_tiles_grouped = torch.ops.gq_b200.fused_mul_mat_gguf_tiles_grouped

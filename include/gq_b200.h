@@ -1,0 +1,124 @@
+/*
+ * gq_b200 — C ABI of the B200 (sm_100a) GGUF quantized-linear path.
+ *
+ * Drop-in boundary for the GGUF LinearMethod of the reference's vLLM plugin: everything the plugin's
+ * load step (process_weights_after_loading) and per-call step (apply) hand to a kernel goes through
+ * these entry points.  The reference has no C ABI of its own for this path — its launcher is
+ * Python/Triton (gguf-plugin/gluon/interface.py, gguf-plugin/gluon/tiles_grouped.py) — so each entry
+ * point cites the reference function it replaces.
+ *
+ * Conventions
+ *   - Every function returns an int status: 0 ok; < 0 the arguments were rejected on the host and
+ *     nothing was launched (GQ_ERR_*); > 0 is only ever reported through gq_read_status (a kernel hit a
+ *     bounded wait's limit).  Nothing aborts, traps or spins without a limit.
+ *   - Pointers named *_dev are device pointers owned by the caller; `stream` is a cudaStream_t passed
+ *     as void*.  No entry point allocates or frees device memory, or synchronises, except where stated.
+ *   - GGML type ids: Q4_0 2, Q5_0 6, Q8_0 8, Q2_K 10, Q3_K 11, Q4_K 12, Q5_K 13, Q6_K 14, IQ4_NL 20,
+ *     IQ3_S 21, IQ4_XS 23.  K must be a multiple of 256.
+ *   - Thread safety: re-entrant; one call at a time per workspace buffer.
+ */
+#ifndef GQ_B200_H
+#define GQ_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GQ_ERR_TYPE (-1)        /* unsupported GGML type */
+#define GQ_ERR_SHAPE (-2)       /* K not a multiple of 256, negative sizes, M over the entry point's limit */
+#define GQ_ERR_ARG (-3)         /* null pointer, misaligned pointer, inconsistent descriptor */
+#define GQ_ERR_WORKSPACE (-4)   /* workspace too small */
+#define GQ_ERR_CUDA (-5)        /* a CUDA runtime call failed; see gq_last_cuda_error */
+#define GQ_ERR_LIMIT (-6)       /* size beyond a documented fixed maximum */
+
+#define GQ_DESC_WORDS 8         /* int32 words per descriptor row */
+#define GQ_MAX_GEMV_ROWS 64     /* largest batch gq_gemv_grouped accepts */
+
+/* ---- format facts (host) ---------------------------------------------------------------------- */
+
+/* Bytes of one row's 256-weight segment of raw GGUF blocks; 0 for an unsupported type.
+ * Reference: gguf-plugin/gluon/tiles.py:24-36 (TILE_TYPES block sizes), kq_tiles.py:22, q2k.py:34. */
+int gq_bytes_per_256(int type);
+
+/* Bytes of the packed (tile-major) form of an [n_out, K] tensor: ceil(n_out/64) * (K/256) * 64 *
+ * bytes_per_256.  < 0 on a bad argument.
+ * Reference: the tile tensor shape [ceil(n/64), nb, 64, row_bytes] of gguf-plugin/gluon/tiles.py:128-130. */
+int64_t gq_packed_bytes(int type, int64_t n_out, int64_t K);
+
+/* The repack map of one 16-row slab: map[p] = row * bytes_per_256 + byte for packed byte p,
+ * 0 <= p < 16 * bytes_per_256 (a permutation).  `map` has room for 16 * bytes_per_256 int32.
+ * Reference: kq_tiles.tile_map (gguf-plugin/test_gguf_rco_cpu.py:255-266 checks its map the same way). */
+int gq_slab_map(int type, int32_t *map);
+
+/* ---- load time --------------------------------------------------------------------------------- */
+
+/* Raw GGUF rows -> packed tiles.  raw_dev: uint8 [n_out, (K/256)*bytes_per_256], row stride
+ * raw_row_stride bytes (>= the row's bytes; any alignment).  out_dev: gq_packed_bytes bytes, 16-byte
+ * aligned.  Rows past n_out in the last tile are written as zeros.
+ * Reference: repack_tiles (gguf-plugin/gluon/tiles.py:128-130) called from _create_tiles
+ * (gguf-plugin/patches/gguf-tiles-all-types.patch:73-131). */
+int gq_repack(int type, const void *raw_dev, int64_t n_out, int64_t K, int64_t raw_row_stride, void *out_dev, void *stream);
+
+/* Packed tiles -> raw GGUF rows (bit-exact inverse of gq_repack).
+ * Reference: unrepack_tiles (gguf-plugin/gluon/tiles.py:39-67, kq_tiles.py:100-125). */
+int gq_unrepack(int type, const void *tiles_dev, int64_t n_out, int64_t K, void *raw_dev, int64_t raw_row_stride, void *stream);
+
+/* Packed tiles -> dequantised weights [n_out, K], row stride ld elements.  out_dtype 0: fp32, every
+ * value bit-identical to gguf.quants.dequantize; 1: bf16 (the fp32 value rounded to nearest even).
+ * Reference: dequantize_tiles (gguf-plugin/gluon/tiles.py:141-149), dequantize_iq3s_tiles
+ * (gguf-plugin/gluon/iq3s_tile_dequant.py:22-63). */
+int gq_dequant(int type, const void *tiles_dev, int64_t n_out, int64_t K, void *out_dev, int out_dtype, int64_t ld, void *stream);
+
+/* Descriptor table of a run of shards that share K and sit back to back in one packed buffer
+ * (shard i's tiles start at byte offset sum_{j<i} gq_packed_bytes(j)).  One row of GQ_DESC_WORDS int32
+ * per (64-row tile, k-range): {tile byte offset / 16, type, first output column, valid rows, kb0, kb1,
+ * split index, 0}.  k-ranges are the balanced partition [(s*nb)/S, ((s+1)*nb)/S).  Host function;
+ * desc_host has room for gq_desc_rows(...) rows.  Returns the number of rows written, or < 0.
+ * Reference: descriptors / prepare_grouped_layer (gguf-plugin/gluon/tiles_grouped.py:253-299). */
+int64_t gq_desc_rows(int n_shards, const int64_t *n_outs, int split);
+int64_t gq_build_descs(int n_shards, const int32_t *types, const int64_t *n_outs, int64_t K, int split, int32_t *desc_host);
+
+/* Split-K of a grouped launch: n_tiles output tiles, nb k-blocks, M batch rows, avg_bytes_per_256 of
+ * the run, on a device with sm_count SMs.  Always in [1, nb].
+ * Reference: grouped_split_for (gguf-plugin/gluon/tiles_grouped.py:209-250), re-derived for 148 SMs. */
+int gq_split_for(int64_t n_tiles, int64_t nb, int64_t M, int avg_bytes_per_256, int sm_count);
+
+/* Facts of a run the launcher sizes shared memory by: (largest bytes_per_256 of the run's types) |
+ * (1 << 16 if the run holds an IQ3_S shard).  < 0 on an unsupported type.
+ * Reference: meta["max_rw"] and the NEW mask (gguf-plugin/gluon/tiles_grouped.py:181-202,1239-1265). */
+int gq_run_info(int n_shards, const int32_t *types);
+
+/* ---- per call ---------------------------------------------------------------------------------- */
+
+/* Workspace bytes a call with these sizes needs (activation staging, split-K partials, status). */
+int64_t gq_workspace_bytes(int64_t M, int64_t K, int64_t n_total, int split);
+
+/* Y[M, n_total] = X[M, K] . W^T for a run of packed shards, 1 <= M <= GQ_MAX_GEMV_ROWS.
+ *   x_dev     bf16 [M, K], row stride ldx elements
+ *   packed_dev, desc_dev, n_desc, split   the run's tiles and the descriptor table built for `split`
+ *   run_info  gq_run_info of the run's types
+ *   y_dev     bf16, row stride ldy elements; the run writes columns [0, n_total)
+ *   workspace_dev  at least gq_workspace_bytes(M, K, n_total, split) bytes, 256-byte aligned
+ * Launches: activation preparation, the grouped kernel, and (split > 1) the partial sum.  M == 0 is a
+ * no-op.  Reference: gluon_mul_mat_tiles_grouped for M <= 32 and the bm-64 wide form
+ * (gguf-plugin/gluon/interface.py:141-188), quantize_activations_256, grouped_gemm, sum_partials
+ * (gguf-plugin/gluon/tiles_grouped.py:110-162,1204-1275). */
+int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                    int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
+                    int64_t workspace_bytes, void *stream);
+
+/* Reads the device status word of the last call on this workspace (synchronises the stream): 0, or
+ * a positive GQ_DEV_* code (1: a bounded wait ran out). */
+int gq_read_status(const void *workspace_dev, int64_t workspace_bytes, void *stream);
+
+/* Text of the last CUDA runtime error seen by this library in the calling thread ("" if none). */
+const char *gq_last_cuda_error(void);
+
+/* Number of kernels this library has launched in the calling process (for benchmark bookkeeping). */
+int64_t gq_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GQ_B200_H */
