@@ -1,0 +1,299 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF quantized-linear path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--m 8] [--layers 64]
+
+Workload (config.workload): the mixed-type 64-layer decoder linear stack (hidden 5120, 40 q / 8 kv heads
+of 128, intermediate 17408; eleven GGML types, about 3.88 bits per weight, 10.25 GB of raw block bytes)
+at decode batch M = 8.  A step is one pass of all 256 linears over one batch of synthetic bf16
+activations.  `value` is GB/s of raw GGUF block bytes (the reference's convention for its decode kernel)
+with inputs resident in HBM, the step replayed as one CUDA graph; `e2e` is the same metric through
+GGUFLinearMethod.apply with pinned host inputs copied in and the result copied out inside the timed
+region.  With N > 1 the stack is tensor-parallel (column-split qkv / gate_up, row-split o / down, one
+NCCL all-reduce per row-parallel layer) and the whole job's bytes are divided by the slowest rank's time
+(strong scaling).  `--impl reference` times the CPU restatement of the reference's dequantise-and-multiply
+path on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode GEMV HBM GB/s of raw GGUF block bytes (mixed-type 64-layer linear stack)"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+                for n, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(m: int, n_layers: int, threads_note: bool = True):
+    """The CPU path on a bounded sample: the first n_layers blocks of the stack (same type draw, seeded
+    random valid blocks), x . dequantize(W)^T fused in C with all host threads.  Returns (GB/s, dict)."""
+    import numpy as np
+
+    from hyperqwen_rtx4080s32_b200 import formats as F
+    from hyperqwen_rtx4080s32_b200 import stack as S
+    from hyperqwen_rtx4080s32_b200 import synth
+    from oracle import oracle
+
+    types = S.draw_types(64)[:n_layers]
+    shapes = {"q": (5120, 5120), "k": (1024, 5120), "v": (1024, 5120), "o": (5120, 5120), "gate": (17408, 5120),
+              "up": (17408, 5120), "down": (5120, 17408)}
+    tensors, nbytes = [], 0
+    for li, t in enumerate(types):
+        for name in S.TENSORS:
+            n_out, k = shapes[name]
+            raw = synth.random_blocks(n_out, k, t[name], seed=1000 * li + 10 * S.TENSORS.index(name)).numpy()
+            tensors.append((raw, t[name], k))
+            nbytes += raw.size
+    xs = {k: synth.activations(m, k).float().numpy() for k in (5120, 17408)}
+    oracle.lib()
+    t0 = time.perf_counter()
+    for raw, wt, k in tensors:
+        oracle.matmul_c(xs[k], raw, wt)
+    dt = time.perf_counter() - t0
+    info = {"cores": oracle.num_threads(), "kind": "port",
+            "sample": f"{n_layers} of 64 blocks ({nbytes / 1e6:.0f} MB of raw blocks) at M={m}, fused dequantise-and-dot in C (OpenMP), {dt:.2f} s"}
+    return nbytes / dt / 1e9, dt, info
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(args.warmup):
+        cpu_sample(args.m, 1)
+    times = []
+    for _ in range(args.steps):
+        v, dt, info = cpu_sample(args.m, 1)
+        vals.append(v); times.append(dt)
+    value = statistics.mean(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(times), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"mixed-type 64-layer GGUF linear stack, decode M={args.m}; each step a bounded sample: 1 of 64 blocks on the host cores"},
+            "cpu_baseline": dict(info, value=value, unit="GB/s"),
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from hyperqwen_rtx4080s32_b200 import _lib, ops
+    from hyperqwen_rtx4080s32_b200 import stack as S
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the quantized-linear path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+    st = S.LinearStack(n_layers=args.layers, device=dev, tp_rank=rank, tp_size=world)
+    m = args.m
+    x_dev = st.make_inputs(m)
+    x_host = {k: v.cpu().pin_memory() for k, v in x_dev.items()}
+    out_host = torch.empty((m, st.hidden), dtype=torch.bfloat16).pin_memory()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # warm-up (eager), then capture the step as one CUDA graph
+    for _ in range(max(3, args.warmup)):
+        out = st.step(x_dev)
+    torch.cuda.synchronize()
+    launches0 = L.gq_launch_count()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        st.step(x_dev)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            out = st.step(x_dev)
+    torch.cuda.current_stream().wait_stream(side)
+    launches_per_step = (L.gq_launch_count() - launches0) // 2
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    barrier()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    with ClockSampler(local) as clk:
+        ms_step = timed(graph.replay, args.steps)
+
+    def e2e_step():
+        for k in x_dev:
+            x_dev[k].copy_(x_host[k], non_blocking=True)
+        graph.replay()
+        out_host.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    h2d = sum(v.numel() * 2 for v in x_host.values())
+    d2h = out_host.numel() * 2
+
+    # the grouped kernel alone (activations prepared beforehand): the roofline's launch time
+    runs = []
+    for blk in st.layers:
+        for name in ("qkv", "o", "gate_up", "down"):
+            lin = blk[name]
+            for first, (packed, descs, splits, run, nb, block_bytes) in lin.gguf_groups.items():
+                n_outs = [lin.gguf_tiles_rows[i] for i in run]
+                wts = [lin.gguf_tiles_types[i] for i in run]
+                n_tiles = sum(-(-n // 64) for n in n_outs)
+                s = ops.grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=ops.sm_count(dev))
+                s = s if s in splits else 1
+                nt = sum(n_outs)
+                ws = torch.empty(L.gq_workspace_bytes(m, nb * 256, nt, s), dtype=torch.uint8, device=dev)
+                y = torch.empty((m, nt), dtype=torch.bfloat16, device=dev)
+                runs.append((x_dev[name], packed, descs[splits.index(s)], s, wts, nt, y, ws))
+    for r in runs:
+        ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=1)
+    kgraph = torch.cuda.CUDAGraph()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for r in runs:
+            ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=2)
+        side.synchronize()
+        with torch.cuda.graph(kgraph, stream=side):
+            for r in runs:
+                ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=2)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        kgraph.replay()
+    ms_kernel = timed(kgraph.replay, args.steps)
+
+    if rank == 0:
+        peaks, which = measured_peaks()
+        total_bytes = st.raw_bytes_full
+        value = total_bytes / (ms_step * 1e-3) / 1e9
+        e2e = total_bytes / (ms_e2e * 1e-3) / 1e9
+        achieved = st.raw_bytes_local / (ms_kernel * 1e-3) / 1e9
+        line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32",
+                "data": "synthetic",
+                "config": {"workload": f"mixed-type {args.layers}-layer GGUF decoder linear stack (BASELINE configs[3]{'/[4] tensor-parallel' if world > 1 else ''}), decode M={m}",
+                           "bits_per_weight": round(8 * total_bytes / st.weights_full, 3), "raw_block_bytes": total_bytes,
+                           "l2": "weights (10 GB) far exceed L2; no flush needed", "parallelism": f"tp{world}",
+                           "weights": "random valid blocks (the reference's test method), seeded"},
+                "tokens_per_s": m / (ms_step * 1e-3),
+                "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
+                        "tokens_per_s": m / (ms_e2e * 1e-3)},
+                "gpu_launches": int(launches_per_step * args.steps),
+                "roofline": {"bound": "hbm", "kernel": "gemv_grouped_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": achieved / peaks["hbm_gbs"], "peak_source": which, "frac_of_nominal_8TBs": achieved / 8000.0,
+                             "launches_per_step": len(runs), "avg_launch_us": 1e3 * ms_kernel / len(runs),
+                             "traffic": None},
+                "clocks": clk.summary()}
+        if world == 1 and not args.no_cpu:
+            v, dt, info = cpu_sample(m, 2)
+            line["cpu_baseline"] = dict(info, value=v, unit="GB/s")
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -34,6 +34,7 @@ SIGNATURES = {
     "gq_run_info": (_i32, [_i32, _vp]),
     "gq_workspace_bytes": (_i64, [_i64, _i64, _i64, _i32]),
     "gq_gemv_grouped": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "gq_gemv_grouped_phases": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _vp, _i32]),
     "gq_read_status": (_i32, [_vp, _i64, _vp]),
     "gq_last_cuda_error": (ctypes.c_char_p, []),
     "gq_launch_count": (_i64, []),

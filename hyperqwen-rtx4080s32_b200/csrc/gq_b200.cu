@@ -665,9 +665,9 @@ extern "C" int gq_run_info(int n_shards, const int32_t *types) {
     return maxb | (iq3s << 16);
 }
 
-extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
-                               int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
-                               int64_t workspace_bytes, void *stream) {
+extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                                      int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                                      void *workspace_dev, int64_t workspace_bytes, void *stream, int phases) {
     if (M < 0 || M > GQ_MAX_GEMV_ROWS || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0 || split < 1) return GQ_ERR_SHAPE;
     if (M == 0 || n_total == 0 || n_desc == 0) return GQ_OK;
     if (!x_dev || !packed_dev || !desc_dev || !y_dev || !workspace_dev) return GQ_ERR_ARG;
@@ -679,8 +679,11 @@ extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t 
     if (int rc = ensure_tables()) return rc;
     cudaStream_t st = (cudaStream_t)stream;
 
-    prep_x_kernel<<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16 *)x_dev, ldx, (int)K, ws.ex, ws.xh, ws.sx, ws.status);
-    GQ_LAUNCHED();
+    if (phases & 1) {
+        prep_x_kernel<<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16 *)x_dev, ldx, (int)K, ws.ex, ws.xh, ws.sx, ws.status);
+        GQ_LAUNCHED();
+    }
+    if (!(phases & 6)) return GQ_OK;
 
     GemvParams p;
     p.packed = (const uint8_t *)packed_dev; p.desc = desc_dev; p.xh = ws.xh; p.sx = ws.sx; p.ex = ws.ex;
@@ -692,20 +695,29 @@ extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t 
     p.has_iq3s = (run_info >> 16) & 1;
     const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
     p.stages = mt == 1 ? 4 : mt == 2 ? 4 : mt == 4 ? 3 : 3;
-    int rc;
-    switch (mt) {
-        case 1: rc = launch_gemv<1>(p, n_desc, st); break;
-        case 2: rc = launch_gemv<2>(p, n_desc, st); break;
-        case 4: rc = launch_gemv<4>(p, n_desc, st); break;
-        default: rc = launch_gemv<8>(p, n_desc, st); break;
+    int rc = GQ_OK;
+    if (phases & 2) {
+        switch (mt) {
+            case 1: rc = launch_gemv<1>(p, n_desc, st); break;
+            case 2: rc = launch_gemv<2>(p, n_desc, st); break;
+            case 4: rc = launch_gemv<4>(p, n_desc, st); break;
+            default: rc = launch_gemv<8>(p, n_desc, st); break;
+        }
     }
     if (rc) return rc;
-    if (split > 1) {
+    if (split > 1 && (phases & 4)) {
         const int64_t n = M * n_total;
         sum_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws.partials, split, M, n_total, (__nv_bfloat16 *)y_dev, ldy);
         GQ_LAUNCHED();
     }
     return GQ_OK;
+}
+
+extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                               int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
+                               int64_t workspace_bytes, void *stream) {
+    return gq_gemv_grouped_phases(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
+                                  workspace_bytes, stream, 7);
 }
 
 extern "C" int gq_read_status(const void *workspace_dev, int64_t workspace_bytes, void *stream) {

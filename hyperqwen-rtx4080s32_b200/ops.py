@@ -131,7 +131,7 @@ def pack_tiles(shards: Sequence[tuple[torch.Tensor, int, int]]):
         if t.shape[0] != -(-n_out // 64) or (nb is not None and t.shape[1] != nb):
             raise GqError("shards of a run must share K and hold ceil(n_out/64) tiles")
         nb = int(t.shape[1])
-    packed = torch.cat([t.reshape(-1) for t, _, _ in shards])
+    packed = shards[0][0].reshape(-1) if len(shards) == 1 else torch.cat([t.reshape(-1) for t, _, _ in shards])
     meta = {"nb": nb, "n_outs": [int(n) for _, n, _ in shards], "types": [int(w) for _, _, w in shards],
             "n_total": sum(int(n) for _, n, _ in shards)}
     return packed, meta
@@ -159,8 +159,10 @@ def prepare_grouped_layer(tiles_list: Sequence[torch.Tensor], n_outs: Sequence[i
 # ---- per call ------------------------------------------------------------------------------------
 
 def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, split: int, wtypes: Sequence[int], n_total: int,
-                 out: torch.Tensor | None = None) -> torch.Tensor:
-    """One grouped launch for 1..64 rows: x bf16 [M, K] -> out bf16 [M, n_total] (out may be a column view)."""
+                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, phases: int = 7) -> torch.Tensor:
+    """One grouped launch for 1..64 rows: x bf16 [M, K] -> out bf16 [M, n_total] (out may be a column view).
+    `workspace` (uint8, 256-byte aligned, at least gq_workspace_bytes) is allocated per call unless given;
+    `phases` selects the launches (1 prepare activations, 2 grouped kernel, 4 partial sum)."""
     _need_cuda(x, "x")
     if x.dtype != torch.bfloat16 or x.dim() != 2:
         raise GqError(f"x must be bf16 [M, K], got {x.dtype} {tuple(x.shape)}")
@@ -177,11 +179,11 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
         return out
     L = lib()
     ws_bytes = check(L.gq_workspace_bytes(m, k, n_total, int(split)), "gq_workspace_bytes")
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    ws = workspace if workspace is not None else torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
-        check(L.gq_gemv_grouped(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc.data_ptr(), int(desc.shape[0]), int(split),
-                                run_info(wtypes), out.data_ptr(), out.stride(0), n_total, ws.data_ptr(), ws_bytes, _stream_ptr(x)),
-              "gq_gemv_grouped")
+        check(L.gq_gemv_grouped_phases(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc.data_ptr(), int(desc.shape[0]), int(split),
+                                       run_info(wtypes), out.data_ptr(), out.stride(0), n_total, ws.data_ptr(), ws.numel(), _stream_ptr(x),
+                                       int(phases)), "gq_gemv_grouped")
     return out
 
 

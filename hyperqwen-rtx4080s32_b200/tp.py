@@ -1,0 +1,73 @@
+"""Tensor-parallel sharding of GGUF tensors for the quantized-linear path.
+
+Column-parallel layers (QKV, gate_up) split output rows; row-parallel layers (o, down) split K and sum
+the ranks' partial outputs with one all-reduce per layer.  Shards are cut from the RAW block bytes before
+the repack, so every rank repacks only what it owns.  vLLM's loader narrows the byte dimension evenly
+(vllm/model_executor/layers/linear.py RowParallelLinear.weight_loader), which cuts a 256-weight superblock
+in half when K / tp is not a multiple of 256 (hidden 5120 or 17408 over 8 ranks: 640 and 2176 weights).
+Here a rank instead keeps every k-block its K range touches, whole, and its activations are zero outside
+the range it owns: the shared block contributes x * w only where x is non-zero, so the sum over ranks is
+unchanged and no block is re-encoded.  The price is reading one shared block twice across two ranks.
+The reference has no tensor-parallel code of its own for this path (docs/multi-gpu.md:8-13 passes
+--tensor-parallel-size through to vLLM).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import formats as F
+
+
+@dataclass
+class KPad:
+    """Where a row-parallel rank's own K range [k0, k1) sits inside the k-blocks it stores."""
+    left: int       # zero columns before the rank's activations
+    own: int        # the rank's K / tp columns
+    total: int      # stored K (a multiple of 256)
+
+
+def row_range(k: int, rank: int, size: int) -> tuple[int, int, int, int]:
+    """(k0, k1, first block, one-past-last block) of a rank's K range."""
+    if k % size:
+        raise ValueError(f"K={k} does not divide over {size} ranks")
+    own = k // size
+    if own % 32:
+        raise ValueError(f"K/tp={own} must be a multiple of 32")
+    k0, k1 = rank * own, (rank + 1) * own
+    return k0, k1, k0 // F.QK, -(-k1 // F.QK)
+
+
+def shard_raw(raw: torch.Tensor, wtype: int, parallel: str, rank: int, size: int):
+    """raw uint8 [n_out, nb * B] of the full tensor -> (this rank's raw rows, KPad or None)."""
+    bb = F.BYTES_PER_256[wtype]
+    n_out, nb = raw.shape[0], raw.shape[1] // bb
+    if parallel == "column":
+        if n_out % size:
+            raise ValueError(f"n_out={n_out} does not divide over {size} ranks")
+        per = n_out // size
+        return raw[rank * per:(rank + 1) * per].contiguous(), None
+    if parallel == "row":
+        k0, k1, b0, b1 = row_range(nb * F.QK, rank, size)
+        shard = raw[:, b0 * bb:b1 * bb].contiguous()
+        return shard, KPad(left=k0 - b0 * F.QK, own=k1 - k0, total=(b1 - b0) * F.QK)
+    raise ValueError(parallel)
+
+
+def pad_input(x: torch.Tensor, pad: KPad | None) -> torch.Tensor:
+    """x [M, K/tp] -> [M, stored K] with zeros outside the rank's own range."""
+    if pad is None or (pad.left == 0 and pad.own == pad.total):
+        return x
+    out = x.new_zeros((x.shape[0], pad.total))
+    out[:, pad.left:pad.left + pad.own] = x
+    return out
+
+
+def all_reduce_(t: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum of the ranks' partial outputs (NCCL over NVLink on GPUs, gloo on CPU)."""
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return t

@@ -108,6 +108,15 @@ int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const 
                     int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
                     int64_t workspace_bytes, void *stream);
 
+/* The same call with its launches selectable: phases bit 0 = activation preparation (x -> workspace),
+ * bit 1 = the grouped kernel, bit 2 = the split-K partial sum.  gq_gemv_grouped is phases = 7.  A caller
+ * that multiplies the same x by several runs prepares once and passes phases = 6 for the others, with the
+ * same workspace (its activation area depends only on M and K); a benchmark times bit 1 alone.
+ * Reference: interface.py:164,174 quantises once per layer call for the same reason. */
+int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                           int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                           void *workspace_dev, int64_t workspace_bytes, void *stream, int phases);
+
 /* Reads the device status word of the last call on this workspace (synchronises the stream): 0, or
  * a positive GQ_DEV_* code (1: a bounded wait ran out). */
 int gq_read_status(const void *workspace_dev, int64_t workspace_bytes, void *stream);

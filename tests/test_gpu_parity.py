@@ -1,0 +1,246 @@
+"""GPU parity tests proper: the CUDA path through the C ABI against the CPU oracle on the same seeded
+inputs.  Dequantisation and repack are bit-exact; GEMM outputs are within the contract's max relative
+error 1e-2 of the fp64 dequantise-then-multiply oracle (bf16 activations, fp32 accumulate, bf16 output)
+and within one bf16 rounding of it."""
+import numpy as np
+import pytest
+import torch
+
+from hyperqwen_rtx4080s32_b200 import formats as F
+from hyperqwen_rtx4080s32_b200 import ops, synth
+from hyperqwen_rtx4080s32_b200.linear import GGUFLinear
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2            # the contract: max |y - y_ref| / max_row |y_ref|
+TOL_TIGHT = 6e-3      # bf16 output rounding (2^-8 of the value) plus fp32 accumulation
+
+
+def dev():
+    return torch.device("cuda", 0)
+
+
+def ref_gemm(x, raw, t):
+    return oracle.matmul_f64(x.float().cpu().numpy(), raw.numpy() if isinstance(raw, torch.Tensor) else raw, t)
+
+
+@pytest.mark.parametrize("t", sorted(F.SUPPORTED_TYPES))
+def test_repack_roundtrip_and_golden_positions(t):
+    bb = F.BYTES_PER_256[t]
+    from hyperqwen_rtx4080s32_b200.hostref import repack_numpy
+
+    for n_out, nb in [(48, 1), (70, 3), (130, 4)]:
+        raw = (torch.arange(n_out * nb * bb, dtype=torch.int64) % 251).to(torch.uint8).reshape(n_out, nb * bb)
+        tiles = ops.repack_tiles(raw.to(dev()), n_out, t)
+        assert tuple(tiles.shape) == (-(-n_out // 64), nb, 64 * bb)
+        assert np.array_equal(tiles.cpu().numpy(), repack_numpy(raw.numpy(), t, ops.slab_map(t)))
+        assert torch.equal(ops.unrepack_tiles(tiles, n_out, t).cpu(), raw)
+    # a strided (row-padded) source
+    wide = torch.zeros((70, 3 * bb + 6), dtype=torch.uint8)
+    wide[:, :3 * bb] = raw[:70, :3 * bb] if raw.shape[0] >= 70 else 0
+    src = wide.to(dev())[:, :3 * bb]
+    assert torch.equal(ops.unrepack_tiles(ops.repack_tiles(src, 70, t), 70, t).cpu(), wide[:, :3 * bb])
+
+
+@pytest.mark.parametrize("t", sorted(F.SUPPORTED_TYPES))
+def test_dequant_bit_exact(t, golden):
+    name = F.TYPE_NAMES[t]
+    for key in (f"gguf_{name}", f"enc_{name}"):
+        raw = torch.from_numpy(golden[key + "_raw"])
+        tiles = ops.repack_tiles(raw.to(dev()), raw.shape[0], t)
+        w = ops.dequantize_tiles(tiles, raw.shape[0], 512, t).cpu().numpy()
+        assert np.array_equal(w.view(np.uint32), golden[key + "_w"].view(np.uint32))
+        wb = ops.dequantize_tiles(tiles, raw.shape[0], 512, t, torch.bfloat16).cpu()
+        assert torch.equal(wb, torch.from_numpy(golden[key + "_w"]).to(torch.bfloat16))
+    raw = synth.random_blocks(130, 1024, t, seed=3)
+    w = ops.dequantize_tiles(ops.repack_tiles(raw.to(dev()), 130, t), 130, 1024, t).cpu().numpy()
+    assert np.array_equal(w.view(np.uint32), oracle.dequantize(raw.numpy(), t).view(np.uint32))
+
+
+@pytest.mark.parametrize("t", sorted(F.SUPPORTED_TYPES))
+@pytest.mark.parametrize("shape", [(130, 768), (48, 5120), (1024, 5120)])
+def test_gemv_all_types_all_batches(t, shape):
+    n_out, k = shape
+    raw = synth.random_blocks(n_out, k, t, seed=11 + t)
+    tiles = ops.repack_tiles(raw.to(dev()), n_out, t)
+    packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer([tiles], [n_out], [t])
+    worst = 0.0
+    for m in (1, 2, 4, 8, 16, 17, 32, 33, 64):
+        x = synth.activations(m, k, device=dev())
+        ref = ref_gemm(x, raw, t)
+        for s in sorted(set(splits) | {1, min(2, nb), min(3, nb)}):
+            d = descs[splits.index(s)] if s in splits else torch.from_numpy(ops.build_descs([t], [n_out], k, s)).to(dev())
+            y = ops.grouped_gemm(x, packed, d, s, [t], n_out)
+            y2 = ops.grouped_gemm(x, packed, d, s, [t], n_out)
+            assert torch.equal(y, y2) and not torch.isnan(y).any(), "not deterministic or NaN"
+            err = oracle.rel_err(y.float().cpu().numpy(), ref)
+            worst = max(worst, err)
+            assert err < TOL_TIGHT, f"{F.TYPE_NAMES[t]} {shape} M={m} split={s}: {err:.3e}"
+    assert worst < TOL
+
+
+@pytest.mark.parametrize("t", sorted(F.SUPPORTED_TYPES))
+def test_gemv_encoded_gaussian_weights(t):
+    n_out, k = 256, 1024
+    raw = torch.from_numpy(synth.encoded_weights(n_out, k, t, seed=1000 * t + 4))
+    tiles = ops.repack_tiles(raw.to(dev()), n_out, t)
+    packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer([tiles], [n_out], [t])
+    for m in (1, 8, 64):
+        x = synth.activations(m, k, device=dev())
+        y = ops.mul_mat_tiles_grouped(x, packed, descs, splits, views, [n_out], [t], nb, bb)
+        assert oracle.rel_err(y.float().cpu().numpy(), ref_gemm(x, raw, t)) < TOL_TIGHT
+
+
+def test_activation_range_is_irrelevant():
+    """Activations are rescaled by an exact power of two per row before the fp16 MMA, so tiny, huge and
+    mixed-magnitude bf16 rows all give the same relative accuracy."""
+    t, n_out, k = F.Q4_K, 128, 1024
+    raw = synth.random_blocks(n_out, k, t, seed=5)
+    tiles = ops.repack_tiles(raw.to(dev()), n_out, t)
+    packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer([tiles], [n_out], [t])
+    base = synth.activations(4, k).float()
+    scales = torch.tensor([1e-30, 1.0, 3e4, 1e30]).reshape(4, 1)
+    x = (base * scales).to(torch.bfloat16).to(dev())
+    y = ops.mul_mat_tiles_grouped(x, packed, descs, splits, views, [n_out], [t], nb, bb)
+    assert oracle.rel_err(y.float().cpu().numpy(), ref_gemm(x, raw, t)) < TOL_TIGHT
+    z = torch.zeros((2, k), dtype=torch.bfloat16, device=dev())
+    assert float(ops.mul_mat_tiles_grouped(z, packed, descs, splits, views, [n_out], [t], nb, bb).abs().max()) == 0.0
+
+
+def test_mixed_run_matches_single_shards_bitwise():
+    """A mixed-type run in one launch gives every shard's columns bit-identical to the shard alone at the
+    same split (the reference's check_mixed, test_gluon_kq_gpu.py:172-195)."""
+    k = 1024
+    parts = [(70, F.IQ3_S), (130, F.Q6_K), (48, F.Q2_K), (64, F.IQ4_XS)]
+    raws = [synth.random_blocks(n, k, t, seed=21 + i) for i, (n, t) in enumerate(parts)]
+    tiles = [ops.repack_tiles(r.to(dev()), n, t) for r, (n, t) in zip(raws, parts)]
+    n_outs, wts = [n for n, _ in parts], [t for _, t in parts]
+    packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer(tiles, n_outs, wts)
+    for i, v in enumerate(views):
+        assert torch.equal(v, tiles[i])
+    for m in (1, 8, 32):
+        x = synth.activations(m, k, seed=7 + m, device=dev())
+        for s in (1, 2):
+            d = torch.from_numpy(ops.build_descs(wts, n_outs, k, s)).to(dev())
+            y = ops.grouped_gemm(x, packed, d, s, wts, sum(n_outs))
+            col = 0
+            for (n, t), tl in zip(parts, tiles):
+                d1 = torch.from_numpy(ops.build_descs([t], [n], k, s)).to(dev())
+                y1 = ops.grouped_gemm(x, tl.reshape(-1), d1, s, [t], n)
+                assert torch.equal(y[:, col:col + n], y1), f"shard {F.TYPE_NAMES[t]} differs at M={m} split={s}"
+                col += n
+
+
+def test_output_into_column_view_and_padding_canaries():
+    t, n_out, k = F.Q5_K, 70, 768
+    raw = synth.random_blocks(n_out, k, t, seed=2)
+    tiles = ops.repack_tiles(raw.to(dev()), n_out, t)
+    d = torch.from_numpy(ops.build_descs([t], [n_out], k, 1)).to(dev())
+    x = synth.activations(8, k, device=dev())
+    wide = torch.full((8, n_out + 64), float("nan"), dtype=torch.bfloat16, device=dev())
+    ops.grouped_gemm(x, tiles.reshape(-1), d, 1, [t], n_out, out=wide[:, 32:32 + n_out])
+    assert torch.isnan(wide[:, :32]).all() and torch.isnan(wide[:, 32 + n_out:]).all()      # nothing written outside
+    assert torch.equal(wide[:, 32:32 + n_out], ops.grouped_gemm(x, tiles.reshape(-1), d, 1, [t], n_out))
+
+
+def _layer(shards, k, bias=False):
+    lin = GGUFLinear(k, [n for _, n, _ in shards], bias=bias)
+    raws = {}
+    for sid, n, t in shards:
+        raws[sid] = synth.random_blocks(n, k, t, seed=31 + (hash(str(sid)) % 7) + t)
+        lin.load_shard(raws[sid].to(dev()), t, sid)
+    return lin.to(dev()).finalize(), raws
+
+
+def test_linear_method_single_qkv_gate_up_bias_and_empty_batch():
+    k = 1024
+    cases = [
+        [(None, 130, F.Q4_K)],
+        [("q", 256, F.IQ3_S), ("k", 64, F.Q6_K), ("v", 64, F.Q3_K)],     # mixed types, q k v order
+        [("v", 64, F.Q4_K), ("q", 256, F.Q4_K), ("k", 64, F.Q4_K)],      # same type, loaded out of order
+        [(0, 192, F.IQ4_XS), (1, 192, F.Q2_K)],
+    ]
+    for shards in cases:
+        lin, raws = _layer(shards, k, bias=True)
+        lin.bias.data = torch.randn_like(lin.bias.data.float()).to(torch.bfloat16)
+        order = ["q", "k", "v"] if "q" in raws else [s for s, _, _ in shards]
+        types = {s: t for s, _, t in shards}
+        for m in (0, 1, 8, 64, 150):
+            x = synth.activations(m, k, device=dev()) if m else torch.empty((0, k), dtype=torch.bfloat16, device=dev())
+            y = lin(x)
+            assert tuple(y.shape) == (m, sum(n for _, n, _ in shards)) and y.dtype == torch.bfloat16
+            if m == 0:
+                continue
+            ref = np.concatenate([ref_gemm(x, raws[s], types[s]) for s in order], axis=1) + lin.bias.float().cpu().numpy()
+            assert oracle.rel_err(y.float().cpu().numpy(), ref) < TOL
+        assert lin.weight.data.numel() == 0 or getattr(lin, "gguf_shards", None) is None       # raw rows are freed
+        x3 = synth.activations(6, k, device=dev()).reshape(2, 3, k)
+        assert tuple(lin(x3).shape) == (2, 3, sum(n for _, n, _ in shards))
+
+
+def test_cuda_graph_capture_and_replay():
+    k = 1024
+    lin, raws = _layer([("q", 256, F.Q4_K), ("k", 64, F.IQ3_S), ("v", 64, F.Q8_0)], k)
+    x = synth.activations(8, k, device=dev())
+    eager = lin(x).clone()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        lin(x)
+        s.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            y = lin(x)
+    torch.cuda.current_stream().wait_stream(s)
+    x.copy_(synth.activations(8, k, seed=99, device=dev()))
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y, lin(x)) and not torch.equal(y, eager)
+
+
+def test_fake_impl_shape_and_dtype():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    lin, _ = _layer([(None, 130, F.Q4_K)], 768)
+    packed, descs, splits, run, nb, bb = lin.gguf_groups["__all__"]
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        x = torch.empty((5, 768), dtype=torch.bfloat16, device=dev())
+        y = ops.fused_mul_mat_gguf_tiles_grouped(x, packed, descs, splits, [lin.gguf_tiles["__all__"]], [130], [F.Q4_K], nb, bb)
+    assert tuple(y.shape) == (5, 130) and y.dtype == torch.bfloat16
+
+
+def test_full_size_config0_q4k_properties():
+    """BASELINE configs[0] at full size (K=5120, N=17408, M=1): a row subset against the oracle, plus
+    linearity in x as the size-independent property."""
+    t, n_out, k = F.Q4_K, 17408, 5120
+    raw = synth.random_blocks(n_out, k, t, seed=12000 + 4, device=dev())
+    tiles = ops.repack_tiles(raw, n_out, t)
+    assert torch.equal(ops.unrepack_tiles(tiles, n_out, t), raw)
+    packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer([tiles], [n_out], [t])
+    x = synth.activations(1, k, device=dev())
+    y = ops.mul_mat_tiles_grouped(x, packed, descs, splits, views, [n_out], [t], nb, bb).float().cpu().numpy()
+    rows = np.arange(0, n_out, 97)
+    ref = ref_gemm(x, raw[rows].cpu(), t)
+    assert np.abs(y[:, rows] - ref).max() / np.abs(ref).max() < TOL_TIGHT
+    y2 = ops.mul_mat_tiles_grouped((2 * x.float()).to(torch.bfloat16), packed, descs, splits, views, [n_out], [t], nb, bb).float().cpu().numpy()
+    assert np.abs(y2 - 2 * y).max() <= 2 ** -7 * np.abs(y).max()
+
+
+def test_rejects_bad_arguments_on_the_host(gq_lib):
+    t, n_out, k = F.Q4_K, 64, 768
+    raw = synth.random_blocks(n_out, k, t, seed=1).to(dev())
+    tiles = ops.repack_tiles(raw, n_out, t)
+    d = torch.from_numpy(ops.build_descs([t], [n_out], k, 1)).to(dev())
+    from hyperqwen_rtx4080s32_b200._lib import GqError
+
+    with pytest.raises(GqError):
+        ops.grouped_gemm(torch.zeros((65, k), dtype=torch.bfloat16, device=dev()), tiles.reshape(-1), d, 1, [t], n_out)
+    with pytest.raises(GqError):
+        ops.grouped_gemm(torch.zeros((1, k), dtype=torch.float16, device=dev()), tiles.reshape(-1), d, 1, [t], n_out)
+    with pytest.raises(GqError):
+        ops.repack_tiles(raw.cpu(), n_out, t)
+    x = torch.zeros((1, k), dtype=torch.bfloat16, device=dev())
+    ws = torch.empty(256, dtype=torch.uint8, device=dev())
+    with pytest.raises(GqError, match="workspace"):
+        ops.grouped_gemm(x, tiles.reshape(-1), d, 1, [t], n_out, workspace=ws)
+    assert gq_lib.gq_read_status(ws.data_ptr(), 256, 0) >= 0
