@@ -196,29 +196,32 @@ __global__ void __launch_bounds__(256) dequant_kernel(int type, int B, const uin
 struct Workspace {
     int *status;
     float *ex;        // [M]
-    __half *xh;       // [M][K]
-    __half *sx;       // [M][nb][32]: 16 hi then 16 lo
+    uint8_t *xt;      // [nb][M][GQ_XROW_BYTES]: per k-block, per batch row: 256 fp16 | pad | 16 run sums hi | 16 lo
     float *partials;  // [S][M][n_total]
 };
+
+// one batch row of one k-block in the staged activation tile: 256 fp16 activations (512 B), 32 B of padding
+// (row stride 608 B = 96 mod 128, so the rows an MMA reads together sit in distinct banks), then the sixteen
+// 16-weight run sums as fp16 hi parts (32 B) and lo parts (32 B)
+#define GQ_XROW_BYTES 608
+#define GQ_XROW_SX 544
 
 __host__ __device__ inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 
 static int64_t ws_layout(int64_t M, int64_t K, int64_t n_total, int split, void *base, Workspace *ws) {
     int64_t off = 256;
     const int64_t o_ex = off; off = align256(off + M * 4);
-    const int64_t o_xh = off; off = align256(off + M * K * 2);
-    const int64_t o_sx = off; off = align256(off + M * (K / 16) * 2 * 2);
+    const int64_t o_xt = off; off = align256(off + (K / GQ_QK) * M * GQ_XROW_BYTES);
     const int64_t o_p = off; if (split > 1) off = align256(off + (int64_t)split * M * n_total * 4);
     if (ws && base) {
         uint8_t *b = (uint8_t *)base;
-        ws->status = (int *)b; ws->ex = (float *)(b + o_ex); ws->xh = (__half *)(b + o_xh); ws->sx = (__half *)(b + o_sx);
-        ws->partials = (float *)(b + o_p);
+        ws->status = (int *)b; ws->ex = (float *)(b + o_ex); ws->xt = b + o_xt; ws->partials = (float *)(b + o_p);
     }
     return off;
 }
 
-__global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int K, float *__restrict__ ex,
-                                                     __half *__restrict__ xh, __half *__restrict__ sx, int *status) {
+__global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int K, int M, float *__restrict__ ex,
+                                                     uint8_t *__restrict__ xt, int *status) {
     __shared__ float red[8];
     __shared__ float s_scale;
     const int m = blockIdx.x;
@@ -248,22 +251,23 @@ __global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__rest
     }
     __syncthreads();
     const float scale = s_scale;
-    __half *xo = xh + (int64_t)m * K;
-    __half *so = sx + (int64_t)m * (K >> 3);
     for (int r = threadIdx.x; r < nrun; r += 256) {
+        const int kb = r >> 4, rr = r & 15;
+        uint8_t *row = xt + ((int64_t)kb * M + m) * GQ_XROW_BYTES;
+        __half *xo = reinterpret_cast<__half *>(row) + 16 * rr;
         float sum = 0.0f;
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
             const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(xr + 16 * r + j));
             const __half2 h = __floats2half2_rn(v.x * scale, v.y * scale);
-            *reinterpret_cast<__half2 *>(xo + 16 * r + j) = h;
+            *reinterpret_cast<__half2 *>(xo + j) = h;
             sum += __low2float(h) + __high2float(h);
         }
         const __half hi = __float2half_rn(sum);
         const __half lo = __float2half_rn(sum - __half2float(hi));
-        const int kb = r >> 4, rr = r & 15;
-        so[kb * 32 + rr] = hi;
-        so[kb * 32 + 16 + rr] = lo;
+        __half *so = reinterpret_cast<__half *>(row + GQ_XROW_SX);
+        so[rr] = hi;
+        so[16 + rr] = lo;
     }
 }
 
@@ -274,15 +278,12 @@ __global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__rest
 // MMAs with the weights on the M side and the batch rows on the N side (8 batch rows per MMA, MT MMAs deep).
 // Replaces tiles_grouped_kernel / _run (gguf-plugin/gluon/tiles_grouped.py:343-1201).
 // ---------------------------------------------------------------------------------------------------
-#define GQ_XROW_BYTES 544   // 256 fp16 + 32 bytes of padding: the eight batch rows of an MMA hit distinct banks
-#define GQ_SXROW_BYTES 64
 #define GQ_CONSUMER_WARPS 4
 
 struct GemvParams {
     const uint8_t *packed;
     const int32_t *desc;
-    const __half *xh;
-    const __half *sx;
+    const uint8_t *xt;
     const float *ex;
     __nv_bfloat16 *y;
     float *partials;
@@ -304,10 +305,10 @@ struct PairStep {
             dec.template scale<P>(s0, s1);
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt) {
-                float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+                float tmp[4];
                 const uint2 b0 = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES);
                 const uint2 b1 = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES + 32);
-                mma16816(tmp, a[0], b0.x, b0.y);
+                mma16816_z(tmp, a[0], b0.x, b0.y);
                 mma16816(tmp, a[1], b1.x, b1.y);
                 blk[nt][0] = fmaf(s0, tmp[0], blk[nt][0]);
                 blk[nt][1] = fmaf(s0, tmp[1], blk[nt][1]);
@@ -321,9 +322,9 @@ struct PairStep {
                 if (u == 0) dec.template scale<2 * P>(s0, s1); else dec.template scale<2 * P + 1>(s0, s1);
 #pragma unroll
                 for (int nt = 0; nt < MT; ++nt) {
-                    float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+                    float tmp[4];
                     const uint2 b = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES + 32 * u);
-                    mma16816(tmp, a[u], b.x, b.y);
+                    mma16816_z(tmp, a[u], b.x, b.y);
                     blk[nt][0] = fmaf(s0, tmp[0], blk[nt][0]);
                     blk[nt][1] = fmaf(s0, tmp[1], blk[nt][1]);
                     blk[nt][2] = fmaf(s1, tmp[2], blk[nt][2]);
@@ -335,10 +336,9 @@ struct PairStep {
     }
 };
 
-// one k-block of one slab: acc += d * sum_groups(scale * (W_int . x)) - dmin * (mins . run sums)
+// one k-block of one slab: acc += d * sum_groups(scale * (W_int . x)) - sum_sets f * (A'' . run sums)
 template <int TYPE, int MT>
-__device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *xs, const uint8_t *sxs, const DecAux &aux, int lane,
-                                            float (&acc)[MT][4]) {
+__device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *xs, const DecAux &aux, int lane, float (&acc)[MT][4]) {
     Dec<TYPE> dec;
     dec.load(slab, lane, aux);
     const int g = lane >> 2, t = lane & 3;
@@ -355,54 +355,58 @@ __device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *
         acc[nt][2] = fmaf(d1, blk[nt][2], acc[nt][2]);
         acc[nt][3] = fmaf(d1, blk[nt][3], acc[nt][3]);
     }
-    if constexpr (Dec<TYPE>::HAS_MIN) {
-        uint32_t am[4];
-        dec.min_frag(am);
-        float m0, m1;
-        dec.min_scale(m0, m1);
+    constexpr int NC = Dec<TYPE>::NCORR;
+    if constexpr (NC > 0) {
+        uint32_t ac[NC][4];
+        float fc[NC][2];
+        dec.corr(ac, fc);
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt) {
-            float mm[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint8_t *sb = sxs + (nt * 8 + g) * GQ_SXROW_BYTES + 8 * t;
+            const uint8_t *sb = xs + (nt * 8 + g) * GQ_XROW_BYTES + GQ_XROW_SX + 8 * t;
             const uint2 bh = *reinterpret_cast<const uint2 *>(sb);
             const uint2 bl = *reinterpret_cast<const uint2 *>(sb + 32);
-            mma16816(mm, am, bh.x, bh.y);
-            mma16816(mm, am, bl.x, bl.y);
-            acc[nt][0] = fmaf(-m0, mm[0], acc[nt][0]);
-            acc[nt][1] = fmaf(-m0, mm[1], acc[nt][1]);
-            acc[nt][2] = fmaf(-m1, mm[2], acc[nt][2]);
-            acc[nt][3] = fmaf(-m1, mm[3], acc[nt][3]);
+#pragma unroll
+            for (int j = 0; j < NC; ++j) {
+                float mm[4];
+                mma16816_z(mm, ac[j], bh.x, bh.y);
+                mma16816(mm, ac[j], bl.x, bl.y);
+                acc[nt][0] = fmaf(-fc[j][0], mm[0], acc[nt][0]);
+                acc[nt][1] = fmaf(-fc[j][0], mm[1], acc[nt][1]);
+                acc[nt][2] = fmaf(-fc[j][1], mm[2], acc[nt][2]);
+                acc[nt][3] = fmaf(-fc[j][1], mm[3], acc[nt][3]);
+            }
         }
     }
 }
 
 template <int MT>
-__device__ __forceinline__ void slab_kblock_any(int type, const uint8_t *slab, const uint8_t *xs, const uint8_t *sxs, const DecAux &aux,
-                                                int lane, float (&acc)[MT][4]) {
+__device__ __forceinline__ void slab_kblock_any(int type, const uint8_t *slab, const uint8_t *xs, const DecAux &aux, int lane,
+                                                float (&acc)[MT][4]) {
     switch (type) {
-        case GQ_Q4_0: slab_kblock<GQ_Q4_0, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_Q5_0: slab_kblock<GQ_Q5_0, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_Q8_0: slab_kblock<GQ_Q8_0, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_Q2_K: slab_kblock<GQ_Q2_K, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_Q3_K: slab_kblock<GQ_Q3_K, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_Q4_K: slab_kblock<GQ_Q4_K, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_Q5_K: slab_kblock<GQ_Q5_K, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_Q6_K: slab_kblock<GQ_Q6_K, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_IQ4_NL: slab_kblock<GQ_IQ4_NL, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_IQ3_S: slab_kblock<GQ_IQ3_S, MT>(slab, xs, sxs, aux, lane, acc); break;
-        case GQ_IQ4_XS: slab_kblock<GQ_IQ4_XS, MT>(slab, xs, sxs, aux, lane, acc); break;
+        case GQ_Q4_0: slab_kblock<GQ_Q4_0, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_Q5_0: slab_kblock<GQ_Q5_0, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_Q8_0: slab_kblock<GQ_Q8_0, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_Q2_K: slab_kblock<GQ_Q2_K, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_Q3_K: slab_kblock<GQ_Q3_K, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_Q4_K: slab_kblock<GQ_Q4_K, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_Q5_K: slab_kblock<GQ_Q5_K, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_Q6_K: slab_kblock<GQ_Q6_K, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_IQ4_NL: slab_kblock<GQ_IQ4_NL, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_IQ3_S: slab_kblock<GQ_IQ3_S, MT>(slab, xs, aux, lane, acc); break;
+        case GQ_IQ4_XS: slab_kblock<GQ_IQ4_XS, MT>(slab, xs, aux, lane, acc); break;
     }
 }
 
 template <int MT>
 __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: [stages x (weights wbytes_max | x tile | sx tile)] [full barriers] [empty barriers] [IQ3_S grid]
-    const int xbytes = 8 * MT * GQ_XROW_BYTES, sxbytes = 8 * MT * GQ_SXROW_BYTES;
-    const int stage_bytes = p.wbytes_max + xbytes + sxbytes;
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)p.stages * stage_bytes);
-    uint64_t *empty = full + p.stages;
-    uint2 *grid_s = reinterpret_cast<uint2 *>(empty + p.stages);
+    // layout: [stages x (weights wbytes_max | activation tile)] [full barriers] [empty barriers] [IQ3_S grid]
+    const int stages = p.stages, wmax = p.wbytes_max, M = p.M;
+    const int xbytes = 8 * MT * GQ_XROW_BYTES;
+    const int stage_bytes = wmax + xbytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)stages * stage_bytes);
+    uint64_t *empty = full + stages;
+    uint2 *grid_s = reinterpret_cast<uint2 *>(empty + stages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int32_t *d = p.desc + (int64_t)blockIdx.x * GQ_DESC_WORDS;
@@ -413,7 +417,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
     const int nk = kb1 - kb0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, GQ_CONSUMER_WARPS); }
+        for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, GQ_CONSUMER_WARPS); }
         fence_barrier_init();
     }
     if (p.has_iq3s && type == GQ_IQ3_S) {
@@ -428,24 +432,18 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
     __syncthreads();
 
     if (warp == GQ_CONSUMER_WARPS) {
-        // ---- producer ----
-        const uint8_t *src = p.packed + off + (int64_t)kb0 * tile_bytes;
-        const uint32_t tx = (uint32_t)tile_bytes + (uint32_t)p.M * (512u + GQ_SXROW_BYTES);
-        for (int i = 0; i < nk; ++i) {
-            const int s = i % p.stages;
-            if (i >= p.stages) {
-                if (!mbar_wait(empty + s, ((i / p.stages) - 1) & 1)) { if (lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT); break; }
-            }
-            uint8_t *st = smem + (size_t)s * stage_bytes;
-            if (lane == 0) {
-                mbar_expect_tx(full + s, tx);
+        // ---- producer: one thread; per k-block one bulk copy of the weight tile and one of the activation tile ----
+        if (lane == 0) {
+            const uint8_t *src = p.packed + off + (int64_t)kb0 * tile_bytes;
+            const uint32_t abytes = (uint32_t)M * GQ_XROW_BYTES;
+            const uint8_t *xsrc = p.xt + (int64_t)kb0 * abytes;
+            for (int i = 0, s = 0, round = 0; i < nk; ++i) {
+                if (round > 0 && !mbar_wait(empty + s, (round - 1) & 1)) { atomicExch(p.status, GQ_DEV_TIMEOUT); break; }
+                uint8_t *st = smem + (size_t)s * stage_bytes;
+                mbar_expect_tx(full + s, (uint32_t)tile_bytes + abytes);
                 bulk_g2s(st, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + s);
-            }
-            __syncwarp();
-            const int kb = kb0 + i;
-            for (int n = lane; n < p.M; n += 32) {
-                bulk_g2s(st + p.wbytes_max + n * GQ_XROW_BYTES, p.xh + (int64_t)n * p.K + (int64_t)kb * 256, 512u, full + s);
-                bulk_g2s(st + p.wbytes_max + xbytes + n * GQ_SXROW_BYTES, p.sx + ((int64_t)n * p.nb + kb) * 32, GQ_SXROW_BYTES, full + s);
+                bulk_g2s(st + wmax, xsrc + (int64_t)i * abytes, abytes, full + s);
+                if (++s == stages) { s = 0; ++round; }
             }
         }
         return;
@@ -469,13 +467,14 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
     for (int nt = 0; nt < MT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
     bool ok = true;
-    for (int i = 0; i < nk; ++i) {
-        const int s = i % p.stages;
-        if (!mbar_wait(full + s, (i / p.stages) & 1)) { ok = false; break; }
+    const int slab_off = warp * 16 * B;
+    for (int i = 0, s = 0, round = 0; i < nk; ++i) {
+        if (!mbar_wait(full + s, round & 1)) { ok = false; break; }
         const uint8_t *st = smem + (size_t)s * stage_bytes;
-        slab_kblock_any<MT>(type, st + warp * 16 * B, st + p.wbytes_max, st + p.wbytes_max + xbytes, aux, lane, acc);
+        slab_kblock_any<MT>(type, st + slab_off, st + wmax, aux, lane, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + s);
+        if (++s == stages) { s = 0; ++round; }
     }
     if (!ok) { if (lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT); return; }
 
@@ -635,15 +634,15 @@ extern "C" int64_t gq_workspace_bytes(int64_t M, int64_t K, int64_t n_total, int
 
 template <int MT>
 static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream) {
-    const int xbytes = 8 * MT * GQ_XROW_BYTES, sxbytes = 8 * MT * GQ_SXROW_BYTES;
-    const int stage_bytes = p.wbytes_max + xbytes + sxbytes;
+    const int xbytes = 8 * MT * GQ_XROW_BYTES;
+    const int stage_bytes = p.wbytes_max + xbytes;
     const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? 4096 : 0);
     // opt in once per device to the largest dynamic shared memory any launch of this variant can ask for
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
-        const int max_smem = 4 * (64 * 272 + xbytes + sxbytes) + 4 * 16 + 4096;
+        const int max_smem = 4 * (64 * 272 + xbytes) + 4 * 16 + 4096;
         GQ_CUDA(cudaFuncSetAttribute(gemv_grouped_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem > 232448 ? 232448 : max_smem));
         if (dev < 64) done_mask.fetch_or(1ull << dev);
     }
@@ -680,13 +679,13 @@ extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, i
     cudaStream_t st = (cudaStream_t)stream;
 
     if (phases & 1) {
-        prep_x_kernel<<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16 *)x_dev, ldx, (int)K, ws.ex, ws.xh, ws.sx, ws.status);
+        prep_x_kernel<<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16 *)x_dev, ldx, (int)K, (int)M, ws.ex, ws.xt, ws.status);
         GQ_LAUNCHED();
     }
     if (!(phases & 6)) return GQ_OK;
 
     GemvParams p;
-    p.packed = (const uint8_t *)packed_dev; p.desc = desc_dev; p.xh = ws.xh; p.sx = ws.sx; p.ex = ws.ex;
+    p.packed = (const uint8_t *)packed_dev; p.desc = desc_dev; p.xt = ws.xt; p.ex = ws.ex;
     p.y = (__nv_bfloat16 *)y_dev; p.partials = ws.partials; p.status = ws.status;
     p.M = (int)M; p.K = (int)K; p.nb = (int)(K / GQ_QK); p.split = split; p.ldy = ldy; p.n_total = n_total;
     const int maxb = run_info & 0xFFFF;

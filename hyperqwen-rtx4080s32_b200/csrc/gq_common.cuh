@@ -36,12 +36,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// one poll; the hardware may park the thread for up to about a microsecond before it answers
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
         : "memory");
     return ok != 0;
 }
@@ -66,6 +67,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// d = a . b (no accumulator input: the C operand is one zero register)
+__device__ __forceinline__ void mma16816_z(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 // ---- bit tricks (host fallbacks let the decoders be exercised lane by lane on a CPU) --------------
@@ -118,6 +126,20 @@ GQ_HD inline __half2 u32_as_h2(uint32_t u) { __half2 h; memcpy(&h, &u, 4); retur
 GQ_HD inline float f16lo(uint32_t u) { return __low2float(u32_as_h2(u)); }
 GQ_HD inline float f16hi(uint32_t u) { return __high2float(u32_as_h2(u)); }
 GQ_HD inline float f16bits(uint32_t u16) { return f16lo(u16 & 0xFFFFu); }
+GQ_HD inline float u32_as_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+// byte `j` (0..3) of `word` as a float, minus `off`: the byte is dropped into the mantissa of 2^23 (one prmt)
+// and the constant removed by one add — no integer-to-float conversion instruction
+template <int J>
+GQ_HD inline float byte_f32(uint32_t word, float off = 0.0f) {
+    return u32_as_f32(prmt(word, 0x4B000000u, 0x7440u | J)) - (8388608.0f + off);
+}
+GQ_HD inline uint32_t hmul2(uint32_t a, uint32_t b) {
+#ifdef __CUDA_ARCH__
+    return h2_as_u32(__hmul2(u32_as_h2(a), u32_as_h2(b)));
+#else
+    return h2_as_u32(__floats2half2_rn(f16lo(a) * f16lo(b), f16hi(a) * f16hi(b)));
+#endif
+}
 // packed fp16 arithmetic on raw 32-bit registers; every use in the decoders has an exactly representable result
 GQ_HD inline uint32_t hsub2(uint32_t a, uint32_t b) {
 #ifdef __CUDA_ARCH__
@@ -139,6 +161,7 @@ GQ_HD inline uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
 GQ_HD constexpr uint32_t h2c(uint32_t h16) { return h16 | (h16 << 16); }
 
 #define GQ_MAGIC 0x64006400u    // fp16 (1024, 1024): an integer in the low mantissa bits reads as 1024 + it
+#define GQ_MAGIC64 0x54005400u  // fp16 (64, 64): an integer in mantissa bits 4.. reads as 64 + it
 #define GQ_MAGICB 0x64646464u   // the same high byte in every byte, for prmt (any index 4..7 of the second operand)
 
 }  // namespace gq

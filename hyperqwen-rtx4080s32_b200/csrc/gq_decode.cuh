@@ -8,13 +8,16 @@
 // as packed fp16 pairs, against the B fragment {x[n][16r+4t], x[n][16r+4t+1]}, {x[n][16r+4t+2], x[n][16r+4t+3]}
 // (the k order inside an MMA is free as long as A and B agree, so activations stay in natural order).
 //
-// Every decoder produces the EXACT integer value of the quantised weight (q minus its offset, or the
-// codebook / grid entry with its sign) as fp16 — all of them are below 2048 in magnitude — and hands the
-// scale out separately: an integer (or fp16 d) per 16- or 32-weight group applied to the fp32 MMA result,
-// and the row's fp16 d per k-block.  The minimum term of Q2_K / Q4_K / Q5_K is an extra MMA of the integer
-// mins against per-run activation sums.  The value arithmetic follows the formats as the reference states
-// them (gguf-plugin/gluon/kq_ref.py:17-79, q2k.py:5-12, q4k.py:5-10, iq3s_int8t.py:4-11, iq4xs.py:5-11);
-// Q4_0 / Q5_0 / IQ4_NL, which the reference leaves to the un-vendored plugin, follow gguf-py.
+// Every decoder produces an EXACT integer as fp16 — the quantised field plus a power-of-two bias that
+// comes for free from dropping the field into the mantissa of a constant (1024 + q for a field at bit 0,
+// 64 + q at bit 4, 256 / 16 + q at bits 2 / 6), all below 2048 — and hands the scale out separately: an
+// integer (or fp16 d) per 16- or 32-weight group applied to the fp32 MMA result, and the row's fp16 d per
+// k-block.  Whatever is constant over a 16-weight run — that bias, the format's offset (q - 8, q - 32, ...)
+// and the minimum term of Q2_K / Q4_K / Q5_K — is removed by "correction" MMAs of small exact per-run
+// integers against per-run activation sums:  acc -= f[row] * sum_run A''[row][run] * Sx[run][n].
+// The value arithmetic follows the formats as the reference states them (gguf-plugin/gluon/kq_ref.py:17-79,
+// q2k.py:5-12, q4k.py:5-10, iq3s_int8t.py:4-11, iq4xs.py:5-11); Q4_0 / Q5_0 / IQ4_NL, which the reference
+// leaves to the un-vendored plugin, follow gguf-py.
 #pragma once
 #include "gq_common.cuh"
 
@@ -40,33 +43,31 @@ GQ_HD inline uint32_t w4(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ?
 GQ_HD inline float u8f(uint32_t word, int byte) { return (float)((word >> (8 * byte)) & 0xFFu); }
 GQ_HD inline float s8f(uint32_t word, int byte) { return (float)(int)(int8_t)((word >> (8 * byte)) & 0xFFu); }
 
-// nibble-pair word (bytes hold weights i0,i2,i1,i3): low nibbles -> `lo`, high nibbles -> `hi`, each as
-// {(i0,i1), (i2,i3)} fp16 pairs of (nibble - OFF)
-template <int OFF>
-GQ_HD inline void nib_word(uint32_t w, uint32_t (&lo)[2], uint32_t (&hi)[2]) {
-    const uint32_t w8 = w >> 8;
-    lo[0] = hsub2(and_or(w, 0x000f000fu, GQ_MAGIC), h2k(1024 + OFF));
-    lo[1] = hsub2(and_or(w8, 0x000f000fu, GQ_MAGIC), h2k(1024 + OFF));
-    hi[0] = hfma2(and_or(w, 0x00f000f0u, GQ_MAGIC), h2k(0.0625), h2k(-64 - OFF));
-    hi[1] = hfma2(and_or(w8, 0x00f000f0u, GQ_MAGIC), h2k(0.0625), h2k(-64 - OFF));
-}
+// fp16 magic constants: an unsigned field whose lowest bit sits at mantissa bit b reads as 2^(10-b) + field
+#define GQ_MAGIC_B0 0x64006400u   // 1024 + field
+#define GQ_MAGIC_B2 0x5C005C00u   // 256 + field
+#define GQ_MAGIC_B4 0x54005400u   // 64 + field
+#define GQ_MAGIC_B6 0x4C004C00u   // 16 + field
 
 // the IQ4 codebook as unsigned bytes (value + 128) in four registers, filled by the kernel from the
 // generated table
 struct Iq4Table { uint32_t t0, t1, t2, t3; };
 
-// natural-order nibble word through the 16-entry codebook: lo[] / hi[] as above, exact codebook values
+// natural-order nibble word through the 16-entry codebook: lo[] = low nibbles {(i0,i1), (i2,i3)}, hi[] = high
+// nibbles, each as fp16 pairs of 1024 + (codebook value + 128)
 GQ_HD inline void iq4_word(uint32_t w, const Iq4Table &T, uint32_t (&lo)[2], uint32_t (&hi)[2]) {
     const uint32_t s = w & 0x77777777u;
     const uint32_t s2 = and_or(w >> 1, 0x44444444u, 0x32103210u);
     const uint32_t rl = prmt(prmt(T.t0, T.t1, s), prmt(T.t2, T.t3, s), s2);                       // bytes 0,1
     const uint32_t rh = prmt(prmt(T.t0, T.t1, s >> 16), prmt(T.t2, T.t3, s >> 16), s2 >> 16);     // bytes 2,3
-    // rl = (b0.lo, b0.hi, b1.lo, b1.hi) as value + 128
-    lo[0] = hsub2(prmt(rl, GQ_MAGICB, 0x5250u), h2k(1152));
-    lo[1] = hsub2(prmt(rh, GQ_MAGICB, 0x5250u), h2k(1152));
-    hi[0] = hsub2(prmt(rl, GQ_MAGICB, 0x5351u), h2k(1152));
-    hi[1] = hsub2(prmt(rh, GQ_MAGICB, 0x5351u), h2k(1152));
+    lo[0] = prmt(rl, GQ_MAGICB, 0x5250u);
+    lo[1] = prmt(rh, GQ_MAGICB, 0x5250u);
+    hi[0] = prmt(rl, GQ_MAGICB, 0x5351u);
+    hi[1] = prmt(rh, GQ_MAGICB, 0x5351u);
 }
+
+// two bytes j0, j1 of `w` as an fp16 pair of (1024 + byte)
+GQ_HD inline uint32_t bytes_h2(uint32_t w, uint32_t sel) { return prmt(w, GQ_MAGICB, sel); }
 
 struct DecAux {
     const uint2 *iq3s_grid;   // shared memory: 512 entries, {fp16(m0,m1), fp16(m2,m3)}
@@ -76,11 +77,37 @@ struct DecAux {
 template <int TYPE>
 struct Dec;
 
+// the 12 packed scale bytes of Q4_K / Q5_K -> sc[2], mn[2]: eight 6-bit values each, one per byte
+GQ_HD inline void k4_scales(const uint4 &hd, uint32_t (&sc)[2], uint32_t (&mn)[2]) {
+    sc[0] = hd.y & 0x3f3f3f3fu;
+    mn[0] = hd.z & 0x3f3f3f3fu;
+    sc[1] = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u);
+    mn[1] = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
+}
+
+// Q4_K / Q5_K corrections for lane t (runs 4t..4t+3 = groups 2t (low nibbles, bias 1024) and 2t+1 (high, bias 64)):
+// set 0 removes the bias: A'' = 16 sc | sc, factor 64 d;  set 1 is the minimum term: A'' = m, factor dmin
+GQ_HD inline void k4_corr(int t, const uint32_t (&sc)[2][2], const uint32_t (&mn)[2][2], const uint32_t (&dd)[2],
+                          uint32_t (&a)[2][4], float (&f)[2][2]) {
+    const uint32_t j = 2 * (t & 1);
+    const uint32_t s0 = 0x5050u | (j * 0x0101u), s1 = 0x5050u | ((j + 1) * 0x0101u);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t ws = (t & 2) ? sc[h][1] : sc[h][0], wm = (t & 2) ? mn[h][1] : mn[h][0];
+        a[0][h] = hfma2(bytes_h2(ws, s0), h2k(16), h2k(-16384));
+        a[0][2 + h] = hsub2(bytes_h2(ws, s1), h2k(1024));
+        a[1][h] = hsub2(bytes_h2(wm, s0), h2k(1024));
+        a[1][2 + h] = hsub2(bytes_h2(wm, s1), h2k(1024));
+        f[0][h] = 64.0f * f16lo(dd[h]);
+        f[1][h] = f16hi(dd[h]);
+    }
+}
+
 // ---- Q4_K -----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_Q4_K> {
     static constexpr int GROUP = 32;
-    static constexpr bool HAS_MIN = true;
+    static constexpr int NCORR = 2;
     uint4 q[4];
     uint32_t dd[2], sc[2][2], mn[2][2];
     int t;
@@ -92,51 +119,37 @@ struct Dec<GQ_Q4_K> {
         for (int h = 0; h < 2; ++h) {
             const uint4 hd = ld16(slab + 2048 + 16 * ((lane >> 2) + 8 * h));
             dd[h] = hd.x;
-            sc[h][0] = hd.y & 0x3f3f3f3fu;
-            mn[h][0] = hd.z & 0x3f3f3f3fu;
-            sc[h][1] = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u);
-            mn[h][1] = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
+            k4_scales(hd, sc[h], mn[h]);
         }
     }
     // run pair P = (2P, 2P+1): qs group c = P>>1, nibble half = P&1, u = run&1
     template <int P>
     GQ_HD void pair(uint32_t (&a)[2][4]) const {
         constexpr int c = P >> 1, hi = P & 1;
+        constexpr uint32_t mask = hi ? 0x00f000f0u : 0x000f000fu, magic = hi ? GQ_MAGIC_B4 : GQ_MAGIC_B0;
 #pragma unroll
         for (int u = 0; u < 2; ++u)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                uint32_t lo_[2], hi_[2];
-                nib_word<0>(w4(q[c], 2 * h + u), lo_, hi_);
-                a[u][h] = hi ? hi_[0] : lo_[0];
-                a[u][2 + h] = hi ? hi_[1] : lo_[1];
+                const uint32_t w = w4(q[c], 2 * h + u);
+                a[u][h] = and_or(w, mask, magic);
+                a[u][2 + h] = and_or(w >> 8, mask, magic);
             }
     }
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const {
-        s0 = u8f(sc[0][G >> 2], G & 3);
-        s1 = u8f(sc[1][G >> 2], G & 3);
+        s0 = byte_f32<(G & 3)>(sc[0][G >> 2]);
+        s1 = byte_f32<(G & 3)>(sc[1][G >> 2]);
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16lo(dd[0]); d1 = f16lo(dd[1]); }
-    GQ_HD void min_scale(float &m0, float &m1) const { m0 = f16hi(dd[0]); m1 = f16hi(dd[1]); }
-    // integer mins of runs 4t..4t+3 (groups 2t, 2t+1) for rows g (a[0], a[2]) and g+8 (a[1], a[3])
-    GQ_HD void min_frag(uint32_t (&a)[4]) const {
-        const uint32_t j = 2 * (t & 1);
-        const uint32_t s0 = 0x5050u | (j * 0x0101u), s1 = 0x5050u | ((j + 1) * 0x0101u);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t w = (t & 2) ? mn[h][1] : mn[h][0];
-            a[h] = hsub2(prmt(w, GQ_MAGICB, s0), h2k(1024));
-            a[2 + h] = hsub2(prmt(w, GQ_MAGICB, s1), h2k(1024));
-        }
-    }
+    GQ_HD void corr(uint32_t (&a)[2][4], float (&f)[2][2]) const { k4_corr(t, sc, mn, dd, a, f); }
 };
 
 // ---- Q5_K -----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_Q5_K> {
     static constexpr int GROUP = 32;
-    static constexpr bool HAS_MIN = true;
+    static constexpr int NCORR = 2;
     uint4 q[5];
     uint32_t dd[2], sc[2][2], mn[2][2];
     int t;
@@ -148,10 +161,7 @@ struct Dec<GQ_Q5_K> {
         for (int h = 0; h < 2; ++h) {
             const uint4 hd = ld16(slab + 2560 + 16 * ((lane >> 2) + 8 * h));
             dd[h] = hd.x;
-            sc[h][0] = hd.y & 0x3f3f3f3fu;
-            mn[h][0] = hd.z & 0x3f3f3f3fu;
-            sc[h][1] = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u);
-            mn[h][1] = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
+            k4_scales(hd, sc[h], mn[h]);
         }
     }
     template <int P>
@@ -164,48 +174,42 @@ struct Dec<GQ_Q5_K> {
                 const uint32_t w = w4(q[c], 2 * h + u), H = w4(q[4], 2 * h + u);
                 const uint32_t w8 = w >> 8, H8 = H >> 8;
                 if constexpr (!hi) {
-                    a[u][h] = hsub2(or_and(and_or(w, 0x000f000fu, GQ_MAGIC), shl_c<4 - ib>(H), 0x00100010u), h2k(1024));
-                    a[u][2 + h] = hsub2(or_and(and_or(w8, 0x000f000fu, GQ_MAGIC), shl_c<4 - ib>(H8), 0x00100010u), h2k(1024));
+                    a[u][h] = or_and(and_or(w, 0x000f000fu, GQ_MAGIC_B0), shl_c<4 - ib>(H), 0x00100010u);
+                    a[u][2 + h] = or_and(and_or(w8, 0x000f000fu, GQ_MAGIC_B0), shl_c<4 - ib>(H8), 0x00100010u);
                 } else {
-                    a[u][h] = hfma2(or_and(and_or(w, 0x00f000f0u, GQ_MAGIC), shl_c<8 - ib>(H), 0x01000100u), h2k(0.0625), h2k(-64));
-                    a[u][2 + h] = hfma2(or_and(and_or(w8, 0x00f000f0u, GQ_MAGIC), shl_c<8 - ib>(H8), 0x01000100u), h2k(0.0625), h2k(-64));
+                    a[u][h] = or_and(and_or(w, 0x00f000f0u, GQ_MAGIC_B4), shl_c<8 - ib>(H), 0x01000100u);
+                    a[u][2 + h] = or_and(and_or(w8, 0x00f000f0u, GQ_MAGIC_B4), shl_c<8 - ib>(H8), 0x01000100u);
                 }
             }
     }
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const {
-        s0 = u8f(sc[0][G >> 2], G & 3);
-        s1 = u8f(sc[1][G >> 2], G & 3);
+        s0 = byte_f32<(G & 3)>(sc[0][G >> 2]);
+        s1 = byte_f32<(G & 3)>(sc[1][G >> 2]);
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16lo(dd[0]); d1 = f16lo(dd[1]); }
-    GQ_HD void min_scale(float &m0, float &m1) const { m0 = f16hi(dd[0]); m1 = f16hi(dd[1]); }
-    GQ_HD void min_frag(uint32_t (&a)[4]) const {
-        const uint32_t j = 2 * (t & 1);
-        const uint32_t s0 = 0x5050u | (j * 0x0101u), s1 = 0x5050u | ((j + 1) * 0x0101u);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t w = (t & 2) ? mn[h][1] : mn[h][0];
-            a[h] = hsub2(prmt(w, GQ_MAGICB, s0), h2k(1024));
-            a[2 + h] = hsub2(prmt(w, GQ_MAGICB, s1), h2k(1024));
-        }
-    }
+    GQ_HD void corr(uint32_t (&a)[2][4], float (&f)[2][2]) const { k4_corr(t, sc, mn, dd, a, f); }
 };
 
 // ---- Q6_K -----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_Q6_K> {
     static constexpr int GROUP = 16;
-    static constexpr bool HAS_MIN = false;
+    static constexpr int NCORR = 1;
     uint4 q[6];
-    uint4 sc[2];
+    uint4 sc[2];      // int8 scales + 128 (unsigned bytes)
     uint32_t dd[2];
+    int t;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux &) {
+        t = lane & 3;
 #pragma unroll
         for (int c = 0; c < 6; ++c) q[c] = ld16(slab + 512 * c + 16 * lane);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int row = (lane >> 2) + 8 * h;
-            sc[h] = ld16(slab + 3072 + 16 * row);
+            uint4 s = ld16(slab + 3072 + 16 * row);
+            s.x ^= 0x80808080u; s.y ^= 0x80808080u; s.z ^= 0x80808080u; s.w ^= 0x80808080u;
+            sc[h] = s;
             dd[h] = ld2(slab + 3072 + 256 + 2 * row);
         }
     }
@@ -220,30 +224,62 @@ struct Dec<GQ_Q6_K> {
                 const uint32_t w = w4(q[2 * hp + (tp & 1)], 2 * h + u), H = w4(q[4 + hp], 2 * h + u);
                 const uint32_t w8 = w >> 8, H8 = H >> 8;
                 if constexpr (!hi) {
-                    a[u][h] = hsub2(or_and(and_or(w, 0x000f000fu, GQ_MAGIC), shl_c<4 - 2 * tp>(H), 0x00300030u), h2k(1056));
-                    a[u][2 + h] = hsub2(or_and(and_or(w8, 0x000f000fu, GQ_MAGIC), shl_c<4 - 2 * tp>(H8), 0x00300030u), h2k(1056));
+                    a[u][h] = or_and(and_or(w, 0x000f000fu, GQ_MAGIC_B0), shl_c<4 - 2 * tp>(H), 0x00300030u);
+                    a[u][2 + h] = or_and(and_or(w8, 0x000f000fu, GQ_MAGIC_B0), shl_c<4 - 2 * tp>(H8), 0x00300030u);
                 } else {
-                    a[u][h] = hfma2(or_and(and_or(w, 0x00f000f0u, GQ_MAGIC), shl_c<8 - 2 * tp>(H), 0x03000300u), h2k(0.0625), h2k(-96));
-                    a[u][2 + h] = hfma2(or_and(and_or(w8, 0x00f000f0u, GQ_MAGIC), shl_c<8 - 2 * tp>(H8), 0x03000300u), h2k(0.0625), h2k(-96));
+                    a[u][h] = or_and(and_or(w, 0x00f000f0u, GQ_MAGIC_B4), shl_c<8 - 2 * tp>(H), 0x03000300u);
+                    a[u][2 + h] = or_and(and_or(w8, 0x00f000f0u, GQ_MAGIC_B4), shl_c<8 - 2 * tp>(H8), 0x03000300u);
                 }
             }
     }
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const {
-        s0 = s8f(w4(sc[0], G >> 2), G & 3);
-        s1 = s8f(w4(sc[1], G >> 2), G & 3);
+        s0 = byte_f32<(G & 3)>(w4(sc[0], G >> 2), 128.0f);
+        s1 = byte_f32<(G & 3)>(w4(sc[1], G >> 2), 128.0f);
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16bits(dd[0]); d1 = f16bits(dd[1]); }
+    // weight = field - 32 with field biased by 1024 (low-nibble runs: t even) or 64 (high-nibble runs: t odd):
+    // A'' = sc * 11 | sc, factor 96 d  (1056 = 96 * 11)
+    GQ_HD void corr(uint32_t (&a)[1][4], float (&f)[1][2]) const {
+        const uint32_t mult = (t & 1) ? h2k(1) : h2k(11);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t w = w4(sc[h], t);
+            a[0][h] = hmul2(hsub2(bytes_h2(w, 0x5150u), h2k(1152)), mult);
+            a[0][2 + h] = hmul2(hsub2(bytes_h2(w, 0x5352u), h2k(1152)), mult);
+            f[0][h] = 96.0f * f16bits(dd[h]);
+        }
+    }
 };
+
+// scale of 32-weight block G from a row's eight fp16 d's
+template <int G>
+GQ_HD inline void d8_scale(const uint4 (&d8)[2], float &s0, float &s1) {
+    const uint32_t w0 = w4(d8[0], G >> 1), w1 = w4(d8[1], G >> 1);
+    s0 = (G & 1) ? f16hi(w0) : f16lo(w0);
+    s1 = (G & 1) ? f16hi(w1) : f16lo(w1);
+}
+// correction operand of the legacy types: the fp16 d of blocks 2t (runs 4t, 4t+1) and 2t+1 (runs 4t+2, 4t+3)
+GQ_HD inline void d8_corr(int t, const uint4 (&d8)[2], float bias, uint32_t (&a)[1][4], float (&f)[1][2]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t w = w4(d8[h], t);
+        a[0][h] = prmt(w, w, 0x1010u);
+        a[0][2 + h] = prmt(w, w, 0x3232u);
+        f[0][h] = bias;
+    }
+}
 
 // ---- Q8_0 -----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_Q8_0> {
     static constexpr int GROUP = 32;
-    static constexpr bool HAS_MIN = false;
+    static constexpr int NCORR = 1;
     uint4 q[8];
     uint4 d8[2];
+    int t;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux &) {
+        t = lane & 3;
 #pragma unroll
         for (int c = 0; c < 8; ++c) q[c] = ld16(slab + 512 * c + 16 * lane);
 #pragma unroll
@@ -255,30 +291,25 @@ struct Dec<GQ_Q8_0> {
         for (int u = 0; u < 2; ++u)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint32_t x = w4(q[P], 2 * h + u) ^ 0x80808080u;
-                a[u][h] = hsub2(prmt(x, GQ_MAGICB, 0x5150u), h2k(1152));
-                a[u][2 + h] = hsub2(prmt(x, GQ_MAGICB, 0x5352u), h2k(1152));
+                const uint32_t x = w4(q[P], 2 * h + u) ^ 0x80808080u;    // int8 + 128
+                a[u][h] = prmt(x, GQ_MAGICB, 0x5150u);
+                a[u][2 + h] = prmt(x, GQ_MAGICB, 0x5352u);
             }
     }
     template <int G>
-    GQ_HD void scale(float &s0, float &s1) const {
-        const uint32_t w0 = w4(d8[0], G >> 1), w1 = w4(d8[1], G >> 1);
-        s0 = (G & 1) ? f16hi(w0) : f16lo(w0);
-        s1 = (G & 1) ? f16hi(w1) : f16lo(w1);
-    }
+    GQ_HD void scale(float &s0, float &s1) const { d8_scale<G>(d8, s0, s1); }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 1.0f; d1 = 1.0f; }
+    GQ_HD void corr(uint32_t (&a)[1][4], float (&f)[1][2]) const { d8_corr(t, d8, 1152.0f, a, f); }
 };
 
-// ---- Q4_0 / IQ4_NL (18-byte blocks: d, 16 nibble bytes) ---------------------------------------------
-template <int TYPE>
-struct DecLegacy4 {
+// ---- Q4_0 (18-byte blocks: d, 16 nibble bytes): exact centring, no correction ------------------------
+template <>
+struct Dec<GQ_Q4_0> {
     static constexpr int GROUP = 32;
-    static constexpr bool HAS_MIN = false;
+    static constexpr int NCORR = 0;
     uint4 q[4];
     uint4 d8[2];
-    Iq4Table tab;
-    GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
-        tab = aux.iq4;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux &) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) q[c] = ld16(slab + 512 * c + 16 * lane);
 #pragma unroll
@@ -289,29 +320,56 @@ struct DecLegacy4 {
     GQ_HD void pair(uint32_t (&a)[2][4]) const {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
+            const uint32_t w = w4(q[P >> 1], 2 * h + (P & 1)), w8 = w >> 8;
+            a[0][h] = hsub2(and_or(w, 0x000f000fu, GQ_MAGIC_B0), h2k(1032));
+            a[0][2 + h] = hsub2(and_or(w8, 0x000f000fu, GQ_MAGIC_B0), h2k(1032));
+            a[1][h] = hsub2(and_or(w, 0x00f000f0u, GQ_MAGIC_B4), h2k(72));
+            a[1][2 + h] = hsub2(and_or(w8, 0x00f000f0u, GQ_MAGIC_B4), h2k(72));
+        }
+    }
+    template <int G>
+    GQ_HD void scale(float &s0, float &s1) const { d8_scale<G>(d8, s0, s1); }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 1.0f; d1 = 1.0f; }
+};
+
+// ---- IQ4_NL (18-byte blocks: d, 16 codebook-index nibble bytes) --------------------------------------
+template <>
+struct Dec<GQ_IQ4_NL> {
+    static constexpr int GROUP = 32;
+    static constexpr int NCORR = 1;
+    uint4 q[4];
+    uint4 d8[2];
+    Iq4Table tab;
+    int t;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
+        tab = aux.iq4;
+        t = lane & 3;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) q[c] = ld16(slab + 512 * c + 16 * lane);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) d8[h] = ld16(slab + 2048 + 16 * ((lane >> 2) + 8 * h));
+    }
+    template <int P>
+    GQ_HD void pair(uint32_t (&a)[2][4]) const {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
             uint32_t lo_[2], hi_[2];
-            const uint32_t w = w4(q[P >> 1], 2 * h + (P & 1));
-            if constexpr (TYPE == GQ_Q4_0) nib_word<8>(w, lo_, hi_); else iq4_word(w, tab, lo_, hi_);
+            iq4_word(w4(q[P >> 1], 2 * h + (P & 1)), tab, lo_, hi_);
             a[0][h] = lo_[0]; a[0][2 + h] = lo_[1];
             a[1][h] = hi_[0]; a[1][2 + h] = hi_[1];
         }
     }
     template <int G>
-    GQ_HD void scale(float &s0, float &s1) const {
-        const uint32_t w0 = w4(d8[0], G >> 1), w1 = w4(d8[1], G >> 1);
-        s0 = (G & 1) ? f16hi(w0) : f16lo(w0);
-        s1 = (G & 1) ? f16hi(w1) : f16lo(w1);
-    }
+    GQ_HD void scale(float &s0, float &s1) const { d8_scale<G>(d8, s0, s1); }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 1.0f; d1 = 1.0f; }
+    GQ_HD void corr(uint32_t (&a)[1][4], float (&f)[1][2]) const { d8_corr(t, d8, 1152.0f, a, f); }
 };
-template <> struct Dec<GQ_Q4_0> : DecLegacy4<GQ_Q4_0> {};
-template <> struct Dec<GQ_IQ4_NL> : DecLegacy4<GQ_IQ4_NL> {};
 
-// ---- Q5_0 (22-byte blocks: d, qh u32, 16 nibble bytes) ----------------------------------------------
+// ---- Q5_0 (22-byte blocks: d, qh u32, 16 nibble bytes): exact centring, no correction -----------------
 template <>
 struct Dec<GQ_Q5_0> {
     static constexpr int GROUP = 32;
-    static constexpr bool HAS_MIN = false;
+    static constexpr int NCORR = 0;
     uint4 q[4];
     uint4 d8[2];
     uint4 qh[2][2];
@@ -338,18 +396,14 @@ struct Dec<GQ_Q5_0> {
             // i1 -> 16 (and i2, i3 after a shift by 2)
             const uint32_t bl = (H >> (4 * t)) & 0xFu, bh = (H >> (16 + 4 * t)) & 0xFu;
             const uint32_t zl = (bl | (bl << 15)) << 4, zh = (bh | (bh << 15)) << 8;
-            a[0][h] = hsub2(or_and(and_or(w, 0x000f000fu, GQ_MAGIC), zl, 0x00100010u), h2k(1040));
-            a[0][2 + h] = hsub2(or_and(and_or(w8, 0x000f000fu, GQ_MAGIC), zl >> 2, 0x00100010u), h2k(1040));
-            a[1][h] = hfma2(or_and(and_or(w, 0x00f000f0u, GQ_MAGIC), zh, 0x01000100u), h2k(0.0625), h2k(-80));
-            a[1][2 + h] = hfma2(or_and(and_or(w8, 0x00f000f0u, GQ_MAGIC), zh >> 2, 0x01000100u), h2k(0.0625), h2k(-80));
+            a[0][h] = hsub2(or_and(and_or(w, 0x000f000fu, GQ_MAGIC_B0), zl, 0x00100010u), h2k(1040));
+            a[0][2 + h] = hsub2(or_and(and_or(w8, 0x000f000fu, GQ_MAGIC_B0), zl >> 2, 0x00100010u), h2k(1040));
+            a[1][h] = hsub2(or_and(and_or(w, 0x00f000f0u, GQ_MAGIC_B4), zh, 0x01000100u), h2k(80));
+            a[1][2 + h] = hsub2(or_and(and_or(w8, 0x00f000f0u, GQ_MAGIC_B4), zh >> 2, 0x01000100u), h2k(80));
         }
     }
     template <int G>
-    GQ_HD void scale(float &s0, float &s1) const {
-        const uint32_t w0 = w4(d8[0], G >> 1), w1 = w4(d8[1], G >> 1);
-        s0 = (G & 1) ? f16hi(w0) : f16lo(w0);
-        s1 = (G & 1) ? f16hi(w1) : f16lo(w1);
-    }
+    GQ_HD void scale(float &s0, float &s1) const { d8_scale<G>(d8, s0, s1); }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 1.0f; d1 = 1.0f; }
 };
 
@@ -357,16 +411,32 @@ struct Dec<GQ_Q5_0> {
 template <>
 struct Dec<GQ_IQ4_XS> {
     static constexpr int GROUP = 32;
-    static constexpr bool HAS_MIN = false;
+    static constexpr int NCORR = 1;
     uint4 q[4];
-    uint2 hd[2];
+    uint32_t ls[2][2];   // the eight 6-bit sub-block scales of a row as bytes (value + 32)
+    uint32_t dd[2];
     Iq4Table tab;
+    int t;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
         tab = aux.iq4;
+        t = lane & 3;
 #pragma unroll
         for (int c = 0; c < 4; ++c) q[c] = ld16(slab + 512 * c + 16 * lane);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) hd[h] = ld8(slab + 2048 + 8 * ((lane >> 2) + 8 * h));
+        for (int h = 0; h < 2; ++h) {
+            const uint2 hd = ld8(slab + 2048 + 8 * ((lane >> 2) + 8 * h));
+            dd[h] = hd.x;
+            const uint32_t e = hd.y & 0x0f0f0f0fu, o = (hd.y >> 4) & 0x0f0f0f0fu;   // groups 0,2,4,6 | 1,3,5,7
+            const uint32_t sh = hd.x >> 16;
+            // the 2-bit high parts: groups 0..3 from bits 0..7, groups 4..7 from bits 8..15, one per byte
+            uint32_t a0 = (sh | (sh << 12)) & 0x000f000fu;
+            a0 = (a0 | (a0 << 6)) & 0x03030303u;
+            const uint32_t s8 = sh >> 8;
+            uint32_t a1 = (s8 | (s8 << 12)) & 0x000f000fu;
+            a1 = (a1 | (a1 << 6)) & 0x03030303u;
+            ls[h][0] = prmt(e, o, 0x5140u) | (a0 << 4);
+            ls[h][1] = prmt(e, o, 0x7362u) | (a1 << 4);
+        }
     }
     template <int P>
     GQ_HD void pair(uint32_t (&a)[2][4]) const {
@@ -380,23 +450,38 @@ struct Dec<GQ_IQ4_XS> {
     }
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const {
+        s0 = byte_f32<(G & 3)>(ls[0][G >> 2], 32.0f);
+        s1 = byte_f32<(G & 3)>(ls[1][G >> 2], 32.0f);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = f16lo(dd[0]); d1 = f16lo(dd[1]); }
+    // value = 1024 + (codebook + 128): A'' = ls of groups 2t, 2t+1, factor 1152 d
+    GQ_HD void corr(uint32_t (&a)[1][4], float (&f)[1][2]) const {
+        const uint32_t j = 2 * (t & 1);
+        const uint32_t s0 = 0x5050u | (j * 0x0101u), s1 = 0x5050u | ((j + 1) * 0x0101u);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t l = (hd[h].y >> (4 * G)) & 0xFu, hh = (hd[h].x >> (16 + 2 * G)) & 3u;
-            const float v = (float)((int)(l | (hh << 4)) - 32);
-            if (h == 0) s0 = v; else s1 = v;
+            const uint32_t w = (t & 2) ? ls[h][1] : ls[h][0];
+            a[0][h] = hsub2(bytes_h2(w, s0), h2k(1056));
+            a[0][2 + h] = hsub2(bytes_h2(w, s1), h2k(1056));
+            f[0][h] = 1152.0f * f16lo(dd[h]);
         }
     }
-    GQ_HD void kscale(float &d0, float &d1) const { d0 = f16lo(hd[0].x); d1 = f16lo(hd[1].x); }
 };
+
+// multipliers bias/16 of the four runs 4t..4t+3 of the 2-bit types: t even -> bit pairs 0,1 (bias 1024, 256),
+// t odd -> bit pairs 2,3 (bias 64, 16)
+GQ_HD inline void q23_mult(int t, uint32_t &m01, uint32_t &m23) {
+    m01 = (t & 1) ? h2k(4) : h2k(64);
+    m23 = (t & 1) ? h2k(1) : h2k(16);
+}
 
 // ---- Q2_K -----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_Q2_K> {
     static constexpr int GROUP = 16;
-    static constexpr bool HAS_MIN = true;
+    static constexpr int NCORR = 2;
     uint4 q[2];
-    uint4 sc[2];
+    uint4 sc[2], mn[2];   // low / high nibbles of the sixteen scale bytes, one per byte
     uint32_t dd[2];
     int t;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux &) {
@@ -406,7 +491,9 @@ struct Dec<GQ_Q2_K> {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int row = (lane >> 2) + 8 * h;
-            sc[h] = ld16(slab + 1024 + 16 * row);
+            const uint4 s = ld16(slab + 1024 + 16 * row);
+            sc[h] = make_uint4(s.x & 0x0f0f0f0fu, s.y & 0x0f0f0f0fu, s.z & 0x0f0f0f0fu, s.w & 0x0f0f0f0fu);
+            mn[h] = make_uint4((s.x >> 4) & 0x0f0f0f0fu, (s.y >> 4) & 0x0f0f0f0fu, (s.z >> 4) & 0x0f0f0f0fu, (s.w >> 4) & 0x0f0f0f0fu);
             dd[h] = ld4(slab + 1024 + 256 + 4 * row);
         }
     }
@@ -415,29 +502,35 @@ struct Dec<GQ_Q2_K> {
     GQ_HD void pair(uint32_t (&a)[2][4]) const {
         constexpr int n = P >> 2, tp = P & 3;
         constexpr uint32_t mask = 0x00030003u << (2 * tp);
-        constexpr double inv = tp == 0 ? 1.0 : tp == 1 ? 0.25 : tp == 2 ? 0.0625 : 0.015625;
+        constexpr uint32_t magic = tp == 0 ? GQ_MAGIC_B0 : tp == 1 ? GQ_MAGIC_B2 : tp == 2 ? GQ_MAGIC_B4 : GQ_MAGIC_B6;
 #pragma unroll
         for (int u = 0; u < 2; ++u)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint32_t w = w4(q[n], 2 * h + u);
-                a[u][h] = hfma2(and_or(w, mask, GQ_MAGIC), h2k(inv), h2k(-1024 * inv));
-                a[u][2 + h] = hfma2(and_or(w >> 8, mask, GQ_MAGIC), h2k(inv), h2k(-1024 * inv));
+                a[u][h] = and_or(w, mask, magic);
+                a[u][2 + h] = and_or(w >> 8, mask, magic);
             }
     }
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const {
-        s0 = (float)((w4(sc[0], G >> 2) >> (8 * (G & 3))) & 0xFu);
-        s1 = (float)((w4(sc[1], G >> 2) >> (8 * (G & 3))) & 0xFu);
+        s0 = byte_f32<(G & 3)>(w4(sc[0], G >> 2));
+        s1 = byte_f32<(G & 3)>(w4(sc[1], G >> 2));
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16lo(dd[0]); d1 = f16lo(dd[1]); }
-    GQ_HD void min_scale(float &m0, float &m1) const { m0 = f16hi(dd[0]); m1 = f16hi(dd[1]); }
-    GQ_HD void min_frag(uint32_t (&a)[4]) const {
+    // set 0 removes the field bias: A'' = sc * bias/16, factor 16 d;  set 1 is the minimum term: A'' = m, factor dmin
+    GQ_HD void corr(uint32_t (&a)[2][4], float (&f)[2][2]) const {
+        uint32_t m01, m23;
+        q23_mult(t, m01, m23);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t w = (w4(sc[h], t) >> 4) & 0x0f0f0f0fu;   // mins of runs 4t..4t+3
-            a[h] = hsub2(prmt(w, GQ_MAGICB, 0x5150u), h2k(1024));
-            a[2 + h] = hsub2(prmt(w, GQ_MAGICB, 0x5352u), h2k(1024));
+            const uint32_t ws = w4(sc[h], t), wm = w4(mn[h], t);
+            a[0][h] = hmul2(hsub2(bytes_h2(ws, 0x5150u), h2k(1024)), m01);
+            a[0][2 + h] = hmul2(hsub2(bytes_h2(ws, 0x5352u), h2k(1024)), m23);
+            a[1][h] = hsub2(bytes_h2(wm, 0x5150u), h2k(1024));
+            a[1][2 + h] = hsub2(bytes_h2(wm, 0x5352u), h2k(1024));
+            f[0][h] = 16.0f * f16lo(dd[h]);
+            f[1][h] = f16hi(dd[h]);
         }
     }
 };
@@ -446,11 +539,13 @@ struct Dec<GQ_Q2_K> {
 template <>
 struct Dec<GQ_Q3_K> {
     static constexpr int GROUP = 16;
-    static constexpr bool HAS_MIN = false;
+    static constexpr int NCORR = 2;
     uint4 q[3];
-    uint32_t sv[2][4];   // the sixteen 6-bit scales of a row as bytes (value + 32 ... stored value)
+    uint32_t sv[2][4];   // the sixteen 6-bit scales of a row as bytes (value + 32)
     uint32_t dd[2];
+    int t;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux &) {
+        t = lane & 3;
 #pragma unroll
         for (int c = 0; c < 3; ++c) q[c] = ld16(slab + 512 * c + 16 * lane);
 #pragma unroll
@@ -469,33 +564,50 @@ struct Dec<GQ_Q3_K> {
     GQ_HD void pair(uint32_t (&a)[2][4]) const {
         constexpr int n = P >> 2, tp = P & 3;
         constexpr uint32_t mask = 0x00030003u << (2 * tp), hmsk = 0x00040004u << (2 * tp);
-        constexpr double inv = tp == 0 ? 1.0 : tp == 1 ? 0.25 : tp == 2 ? 0.0625 : 0.015625;
+        constexpr uint32_t magic = tp == 0 ? GQ_MAGIC_B0 : tp == 1 ? GQ_MAGIC_B2 : tp == 2 ? GQ_MAGIC_B4 : GQ_MAGIC_B6;
 #pragma unroll
         for (int u = 0; u < 2; ++u)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint32_t w = w4(q[n], 2 * h + u), H = w4(q[2], 2 * h + u);
-                a[u][h] = hfma2(or_and(and_or(w, mask, GQ_MAGIC), shl_c<tp + 2 - 4 * n>(H), hmsk), h2k(inv), h2k(-1024 * inv - 4));
-                a[u][2 + h] = hfma2(or_and(and_or(w >> 8, mask, GQ_MAGIC), shl_c<tp + 2 - 4 * n>(H >> 8), hmsk), h2k(inv), h2k(-1024 * inv - 4));
+                a[u][h] = or_and(and_or(w, mask, magic), shl_c<tp + 2 - 4 * n>(H), hmsk);
+                a[u][2 + h] = or_and(and_or(w >> 8, mask, magic), shl_c<tp + 2 - 4 * n>(H >> 8), hmsk);
             }
     }
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const {
-        s0 = u8f(sv[0][G >> 2], G & 3) - 32.0f;
-        s1 = u8f(sv[1][G >> 2], G & 3) - 32.0f;
+        s0 = byte_f32<(G & 3)>(sv[0][G >> 2], 32.0f);
+        s1 = byte_f32<(G & 3)>(sv[1][G >> 2], 32.0f);
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16bits(dd[0]); d1 = f16bits(dd[1]); }
+    // weight = (q2 + 4 hb) - 4 with the 3-bit field biased by 1024 / 256 / 64 / 16:
+    // set 0: A'' = sc * bias/16, factor 16 d;  set 1: A'' = sc, factor 4 d
+    GQ_HD void corr(uint32_t (&a)[2][4], float (&f)[2][2]) const {
+        uint32_t m01, m23;
+        q23_mult(t, m01, m23);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t w = t == 0 ? sv[h][0] : t == 1 ? sv[h][1] : t == 2 ? sv[h][2] : sv[h][3];
+            a[1][h] = hsub2(bytes_h2(w, 0x5150u), h2k(1056));
+            a[1][2 + h] = hsub2(bytes_h2(w, 0x5352u), h2k(1056));
+            a[0][h] = hmul2(a[1][h], m01);
+            a[0][2 + h] = hmul2(a[1][2 + h], m23);
+            const float d = f16bits(dd[h]);
+            f[0][h] = 16.0f * d;
+            f[1][h] = 4.0f * d;
+        }
+    }
 };
 
 // ---- IQ3_S ----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_IQ3_S> {
     static constexpr int GROUP = 32;
-    static constexpr bool HAS_MIN = false;
+    static constexpr int NCORR = 0;
     uint4 q[2];      // 16 grid-index bytes per row (byte r = run r)
     uint4 sg[2];     // 16 sign bytes per row, pre-shifted so that the lane's nibble is the low one
     uint2 qh[2];     // the eight qh bytes per row, pre-shifted by t
-    uint32_t scw[2], dd[2];
+    uint32_t sce[2], sco[2], dd[2];   // scale nibbles of even / odd sub-blocks, one per byte
     const uint2 *grid;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
         grid = aux.iq3s_grid;
@@ -511,7 +623,9 @@ struct Dec<GQ_IQ3_S> {
             uint2 hq = ld8(slab + 1536 + 8 * row);
             hq.x >>= t; hq.y >>= t;
             qh[h] = hq;
-            scw[h] = ld4(slab + 1664 + 4 * row);
+            const uint32_t scw = ld4(slab + 1664 + 4 * row);
+            sce[h] = scw & 0x0f0f0f0fu;
+            sco[h] = (scw >> 4) & 0x0f0f0f0fu;
             dd[h] = ld2(slab + 1728 + 2 * row);
         }
     }
@@ -534,10 +648,12 @@ struct Dec<GQ_IQ3_S> {
             run<2 * P + 1>(h, a[1][h], a[1][2 + h]);
         }
     }
+    // 1 + 2 s: the nibble dropped into the mantissa of 2^24 (step 2), minus (2^24 - 1)
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const {
-        s0 = (float)(1 + 2 * ((scw[0] >> (4 * G)) & 0xFu));
-        s1 = (float)(1 + 2 * ((scw[1] >> (4 * G)) & 0xFu));
+        constexpr uint32_t sel = 0x7640u | (G >> 1);
+        s0 = u32_as_f32(prmt((G & 1) ? sco[0] : sce[0], 0x4B800000u, sel)) - 16777215.0f;
+        s1 = u32_as_f32(prmt((G & 1) ? sco[1] : sce[1], 0x4B800000u, sel)) - 16777215.0f;
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16bits(dd[0]); d1 = f16bits(dd[1]); }
 };
