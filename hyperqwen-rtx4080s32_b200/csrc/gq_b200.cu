@@ -296,7 +296,7 @@ struct GemvParams {
 
 template <int TYPE, int MT, int P>
 struct PairStep {
-    __device__ __forceinline__ static void run(const Dec<TYPE> &dec, const uint8_t *xs, int g, int t, float (&blk)[MT][4]) {
+    __device__ __forceinline__ static void run(const Dec<TYPE> &dec, const uint8_t *xs, int g, int t, float (&blk)[MT][4], const float (&z)[4]) {
         uint32_t a[2][4];
         dec.template pair<P>(a);
         const uint8_t *xb = xs + g * GQ_XROW_BYTES + 8 * t + 64 * P;   // run 2P at halves 32P + 4t
@@ -308,7 +308,7 @@ struct PairStep {
                 float tmp[4];
                 const uint2 b0 = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES);
                 const uint2 b1 = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES + 32);
-                mma16816_z(tmp, a[0], b0.x, b0.y);
+                mma16816_z(tmp, a[0], b0.x, b0.y, z);
                 mma16816(tmp, a[1], b1.x, b1.y);
                 blk[nt][0] = fmaf(s0, tmp[0], blk[nt][0]);
                 blk[nt][1] = fmaf(s0, tmp[1], blk[nt][1]);
@@ -324,7 +324,7 @@ struct PairStep {
                 for (int nt = 0; nt < MT; ++nt) {
                     float tmp[4];
                     const uint2 b = *reinterpret_cast<const uint2 *>(xb + nt * 8 * GQ_XROW_BYTES + 32 * u);
-                    mma16816_z(tmp, a[u], b.x, b.y);
+                    mma16816_z(tmp, a[u], b.x, b.y, z);
                     blk[nt][0] = fmaf(s0, tmp[0], blk[nt][0]);
                     blk[nt][1] = fmaf(s0, tmp[1], blk[nt][1]);
                     blk[nt][2] = fmaf(s1, tmp[2], blk[nt][2]);
@@ -332,20 +332,21 @@ struct PairStep {
                 }
             }
         }
-        if constexpr (P < 7) PairStep<TYPE, MT, P + 1>::run(dec, xs, g, t, blk);
+        if constexpr (P < 7) PairStep<TYPE, MT, P + 1>::run(dec, xs, g, t, blk, z);
     }
 };
 
 // one k-block of one slab: acc += d * sum_groups(scale * (W_int . x)) - sum_sets f * (A'' . run sums)
 template <int TYPE, int MT>
-__device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *xs, const DecAux &aux, int lane, float (&acc)[MT][4]) {
+__device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *xs, const DecAux &aux, int lane, float (&acc)[MT][4],
+                                            const float (&z)[4]) {
     Dec<TYPE> dec;
     dec.load(slab, lane, aux);
     const int g = lane >> 2, t = lane & 3;
     float blk[MT][4];
 #pragma unroll
     for (int nt = 0; nt < MT; ++nt) blk[nt][0] = blk[nt][1] = blk[nt][2] = blk[nt][3] = 0.f;
-    PairStep<TYPE, MT, 0>::run(dec, xs, g, t, blk);
+    PairStep<TYPE, MT, 0>::run(dec, xs, g, t, blk, z);
     float d0, d1;
     dec.kscale(d0, d1);
 #pragma unroll
@@ -368,7 +369,7 @@ __device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *
 #pragma unroll
             for (int j = 0; j < NC; ++j) {
                 float mm[4];
-                mma16816_z(mm, ac[j], bh.x, bh.y);
+                mma16816_z(mm, ac[j], bh.x, bh.y, z);
                 mma16816(mm, ac[j], bl.x, bl.y);
                 acc[nt][0] = fmaf(-fc[j][0], mm[0], acc[nt][0]);
                 acc[nt][1] = fmaf(-fc[j][0], mm[1], acc[nt][1]);
@@ -379,22 +380,21 @@ __device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *
     }
 }
 
-template <int MT>
-__device__ __forceinline__ void slab_kblock_any(int type, const uint8_t *slab, const uint8_t *xs, const DecAux &aux, int lane,
-                                                float (&acc)[MT][4]) {
-    switch (type) {
-        case GQ_Q4_0: slab_kblock<GQ_Q4_0, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_Q5_0: slab_kblock<GQ_Q5_0, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_Q8_0: slab_kblock<GQ_Q8_0, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_Q2_K: slab_kblock<GQ_Q2_K, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_Q3_K: slab_kblock<GQ_Q3_K, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_Q4_K: slab_kblock<GQ_Q4_K, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_Q5_K: slab_kblock<GQ_Q5_K, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_Q6_K: slab_kblock<GQ_Q6_K, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_IQ4_NL: slab_kblock<GQ_IQ4_NL, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_IQ3_S: slab_kblock<GQ_IQ3_S, MT>(slab, xs, aux, lane, acc); break;
-        case GQ_IQ4_XS: slab_kblock<GQ_IQ4_XS, MT>(slab, xs, aux, lane, acc); break;
+// the consumer loop of one warp for a CTA whose shard is of TYPE: waits for each stage, processes its slab,
+// releases the stage.  Returns false if a bounded wait ran out.
+template <int TYPE, int MT>
+__device__ __forceinline__ bool consume(const uint8_t *smem, uint64_t *full, uint64_t *empty, int stages, int stage_bytes, int wmax,
+                                        int slab_off, int nk, const DecAux &aux, int lane, float (&acc)[MT][4]) {
+    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0, s = 0, round = 0; i < nk; ++i) {
+        if (!mbar_wait(full + s, round & 1)) return false;
+        const uint8_t *st = smem + (size_t)s * stage_bytes;
+        slab_kblock<TYPE, MT>(st + slab_off, st + wmax, aux, lane, acc, z);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+        if (++s == stages) { s = 0; ++round; }
     }
+    return true;
 }
 
 template <int MT>
@@ -468,14 +468,12 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
 
     bool ok = true;
     const int slab_off = warp * 16 * B;
-    for (int i = 0, s = 0, round = 0; i < nk; ++i) {
-        if (!mbar_wait(full + s, round & 1)) { ok = false; break; }
-        const uint8_t *st = smem + (size_t)s * stage_bytes;
-        slab_kblock_any<MT>(type, st + slab_off, st + wmax, aux, lane, acc);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + s);
-        if (++s == stages) { s = 0; ++round; }
+#define GQ_CONSUME(T) case T: ok = consume<T, MT>(smem, full, empty, stages, stage_bytes, wmax, slab_off, nk, aux, lane, acc); break;
+    switch (type) {
+        GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
+        GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS)
     }
+#undef GQ_CONSUME
     if (!ok) { if (lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT); return; }
 
     // ---- epilogue: rows of the MMA are output columns, columns of the MMA are batch rows ----
@@ -693,7 +691,11 @@ extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, i
     p.wbytes_max = 64 * maxb;   // every stage can hold a tile of any shard of the run
     p.has_iq3s = (run_info >> 16) & 1;
     const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
-    p.stages = mt == 1 ? 4 : mt == 2 ? 4 : mt == 4 ? 3 : 3;
+    {
+        // four stages when four CTAs of them still fit an SM's shared memory, else three
+        const int stage_bytes = p.wbytes_max + 8 * mt * GQ_XROW_BYTES;
+        p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? 4096 : 0)) <= 227 * 1024) ? 4 : 3;
+    }
     int rc = GQ_OK;
     if (phases & 2) {
         switch (mt) {
