@@ -154,7 +154,11 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        # graph capture of NCCL collectives: the watchdog thread must not touch CUDA while a capture is open
+        os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     L = _lib.lib()
     st = S.LinearStack(n_layers=args.layers, device=dev, tp_rank=rank, tp_size=world)
     m = args.m
@@ -173,18 +177,34 @@ def run_ours(args):
         out = st.step(x_dev)
     torch.cuda.synchronize()
     launches0 = L.gq_launch_count()
+    out = st.step(x_dev)
+    torch.cuda.synchronize()
+    launches_per_step = L.gq_launch_count() - launches0
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        st.step(x_dev)
-        side.synchronize()
-        with torch.cuda.graph(graph, stream=side):
-            out = st.step(x_dev)
+    captured = 1
+    try:
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                out = st.step(x_dev)
+    except Exception as e:   # noqa: BLE001 - a failed capture falls back to eager stepping on every rank
+        captured = 0
+        print(f"[rank {rank}] CUDA graph capture failed, stepping eagerly: {e}", file=sys.stderr, flush=True)
     torch.cuda.current_stream().wait_stream(side)
-    launches_per_step = (L.gq_launch_count() - launches0) // 2
+    torch.cuda.synchronize()
+    if world > 1:
+        flag = torch.tensor([captured], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        captured = int(flag.item())
+    if captured:
+        run_step = graph.replay
+    else:
+        def run_step():
+            nonlocal out
+            out = st.step(x_dev)
     for _ in range(max(3, args.warmup)):
-        graph.replay()
+        run_step()
     barrier()
 
     def timed(fn, steps):
@@ -203,12 +223,12 @@ def run_ours(args):
         return ms / steps
 
     with ClockSampler(local) as clk:
-        ms_step = timed(graph.replay, args.steps)
+        ms_step = timed(run_step, args.steps)
 
     def e2e_step():
         for k in x_dev:
             x_dev[k].copy_(x_host[k], non_blocking=True)
-        graph.replay()
+        run_step()
         out_host.copy_(out, non_blocking=True)
 
     for _ in range(3):
@@ -260,6 +280,7 @@ def run_ours(args):
                 "config": {"workload": f"mixed-type {args.layers}-layer GGUF decoder linear stack (BASELINE configs[3]{'/[4] tensor-parallel' if world > 1 else ''}), decode M={m}",
                            "bits_per_weight": round(8 * total_bytes / st.weights_full, 3), "raw_block_bytes": total_bytes,
                            "l2": "weights (10 GB) far exceed L2; no flush needed", "parallelism": f"tp{world}",
+                           "cuda_graph": bool(captured),
                            "weights": "random valid blocks (the reference's test method), seeded"},
                 "tokens_per_s": m / (ms_step * 1e-3),
                 "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,

@@ -244,3 +244,31 @@ def test_rejects_bad_arguments_on_the_host(gq_lib):
     with pytest.raises(GqError, match="workspace"):
         ops.grouped_gemm(x, tiles.reshape(-1), d, 1, [t], n_out, workspace=ws)
     assert gq_lib.gq_read_status(ws.data_ptr(), 256, 0) >= 0
+
+
+def test_tensor_parallel_shards_sum_to_the_full_result_on_one_gpu():
+    """The tensor-parallel layout emulated on one GPU: each rank's shard (column-split rows, row-split K with
+    whole k-blocks and zero-padded activations) runs through the kernel; gathered / summed results equal the
+    unsharded oracle product.  tp = 8 makes K / tp = 128-granular (not a multiple of 256)."""
+    from hyperqwen_rtx4080s32_b200 import tp
+
+    k, n = 2048, 256
+    for size in (2, 8):
+        for wtype in (F.Q4_K, F.IQ3_S):
+            raw = synth.random_blocks(n, k, wtype, seed=17)
+            x = synth.activations(8, k)
+            full = ref_gemm(x, raw, wtype)
+            cols, total = [], np.zeros_like(full)
+            for rank in range(size):
+                cs, _ = tp.shard_raw(raw, wtype, "column", rank, size)
+                lin = GGUFLinear(k, [cs.shape[0]])
+                lin.load_shard(cs.to(dev()), wtype)
+                cols.append(lin.finalize()(x.to(dev())).float().cpu().numpy())
+                rs, pad = tp.shard_raw(raw, wtype, "row", rank, size)
+                own = k // size
+                xp = tp.pad_input(x[:, rank * own:(rank + 1) * own].contiguous(), pad).to(dev())
+                lin = GGUFLinear(pad.total, [n])
+                lin.load_shard(rs.to(dev()), wtype)
+                total += lin.finalize()(xp).float().cpu().numpy()
+            assert oracle.rel_err(np.concatenate(cols, axis=1), full) < TOL_TIGHT
+            assert oracle.rel_err(total, full) < TOL          # eight bf16-rounded partial sums
