@@ -296,8 +296,13 @@ def run_ours(args):
             line["cpu_baseline"] = dict(info, value=v, unit="GB/s")
         print(json.dumps(line), flush=True)
     if world > 1:
+        # leave without tearing NCCL down: destroying a process group whose collectives live inside captured
+        # CUDA graphs can block forever, and nothing is left to do
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
