@@ -118,6 +118,8 @@ __global__ void __launch_bounds__(256) unrepack_kernel(int type, int B, const ui
 __constant__ uint32_t c_iq3s_grid[512];
 __constant__ int8_t c_iq4_kvalues[16];
 
+#include "gq_prefill.cuh"
+
 __device__ __forceinline__ float h2f(const uint8_t *p) { return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8)))); }
 
 __device__ __forceinline__ void scale_min_k4(const uint8_t *s, int j, int &sc, int &mn) {
@@ -719,6 +721,67 @@ extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t 
                                int64_t workspace_bytes, void *stream) {
     return gq_gemv_grouped_phases(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
                                   workspace_bytes, stream, 7);
+}
+
+// ---- prefill ----------------------------------------------------------------------------------------
+static int prefill_nb(int64_t M) { return M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+static int64_t pf_ws_layout(int64_t M, int64_t K, int nbt, void *base, int **status, float **ex, uint8_t **xp) {
+    const int64_t mt = (M + nbt - 1) / nbt;
+    int64_t off = 256;
+    const int64_t o_ex = off; off = align256(off + M * 4);
+    off = (off + 1023) & ~(int64_t)1023;
+    const int64_t o_xp = off; off += mt * nbt * K * 2;
+    if (base) { uint8_t *b = (uint8_t *)base; *status = (int *)b; *ex = (float *)(b + o_ex); *xp = b + o_xp; }
+    return off;
+}
+
+extern "C" int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K) {
+    if (M < 0 || K <= 0 || K % GQ_QK) return GQ_ERR_SHAPE;
+    return pf_ws_layout(M, K, prefill_nb(M), nullptr, nullptr, nullptr, nullptr);
+}
+
+template <int NB>
+static int launch_prefill(const PrefillParams &p, const __nv_bfloat16 *x, int64_t ldx, float *ex, uint8_t *xp, cudaStream_t st) {
+    const int mt = (p.M + NB - 1) / NB;
+    const size_t smem = 1024 + (size_t)GQ_PF_STAGES * (GQ_PF_A_BYTES + NB * 128) + 128 + 4096;
+    static std::atomic<unsigned long long> done_mask{0};
+    int dev = 0;
+    GQ_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
+        GQ_CUDA(cudaFuncSetAttribute(gemm_prefill_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev < 64) done_mask.fetch_or(1ull << dev);
+    }
+    prep_x_prefill_kernel<NB><<<(unsigned)(mt * NB), 256, 0, st>>>(x, ldx, p.K, p.M, ex, xp, p.status);
+    GQ_LAUNCHED();
+    gemm_prefill_kernel<NB><<<dim3((unsigned)((p.n_desc + 1) / 2), (unsigned)mt), GQ_PF_THREADS, smem, st>>>(p);
+    GQ_LAUNCHED();
+    return GQ_OK;
+}
+
+extern "C" int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                               int64_t n_desc, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev, int64_t workspace_bytes,
+                               void *stream) {
+    if (M < 0 || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0) return GQ_ERR_SHAPE;
+    if (M == 0 || n_total == 0 || n_desc == 0) return GQ_OK;
+    if (!x_dev || !packed_dev || !desc_dev || !y_dev || !workspace_dev) return GQ_ERR_ARG;
+    if (((uintptr_t)packed_dev & 15) || ((uintptr_t)workspace_dev & 1023) || ((uintptr_t)x_dev & 15) || (ldx & 7) || ldx < K || ldy < n_total)
+        return GQ_ERR_ARG;
+    if (n_desc > 0x7ffffffe || M > (int64_t)65535 * 64) return GQ_ERR_LIMIT;
+    const int nbt = prefill_nb(M);
+    int *status; float *ex; uint8_t *xp;
+    const int64_t need = pf_ws_layout(M, K, nbt, workspace_dev, &status, &ex, &xp);
+    if (workspace_bytes < need) return GQ_ERR_WORKSPACE;
+    if (int rc = ensure_tables()) return rc;
+    PrefillParams p;
+    p.packed = (const uint8_t *)packed_dev; p.desc = desc_dev; p.n_desc = (int)n_desc; p.xp = xp; p.ex = ex;
+    p.y = (__nv_bfloat16 *)y_dev; p.ldy = ldy; p.M = (int)M; p.K = (int)K; p.nb = (int)(K / GQ_QK); p.status = status;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (nbt) {
+        case 64: return launch_prefill<64>(p, (const __nv_bfloat16 *)x_dev, ldx, ex, xp, st);
+        case 128: return launch_prefill<128>(p, (const __nv_bfloat16 *)x_dev, ldx, ex, xp, st);
+        default: return launch_prefill<256>(p, (const __nv_bfloat16 *)x_dev, ldx, ex, xp, st);
+    }
 }
 
 extern "C" int gq_read_status(const void *workspace_dev, int64_t workspace_bytes, void *stream) {

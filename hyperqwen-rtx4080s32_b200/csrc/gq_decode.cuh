@@ -143,6 +143,14 @@ struct Dec<GQ_Q4_K> {
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16lo(dd[0]); d1 = f16lo(dd[1]); }
     GQ_HD void corr(uint32_t (&a)[2][4], float (&f)[2][2]) const { k4_corr(t, sc, mn, dd, a, f); }
+    // for the dequantise-to-fp16 path: integer weight of run R = fragment value - offs<R>();  w = that * (scale * d) - minterm
+    static constexpr bool HAS_MIN = true;
+    template <int R> static constexpr float offs() { return ((R >> 1) & 1) ? 64.0f : 1024.0f; }
+    template <int G>
+    GQ_HD void minterm(float &m0, float &m1) const {
+        m0 = f16hi(dd[0]) * byte_f32<(G & 3)>(mn[0][G >> 2]);
+        m1 = f16hi(dd[1]) * byte_f32<(G & 3)>(mn[1][G >> 2]);
+    }
 };
 
 // ---- Q5_K -----------------------------------------------------------------------------------------
@@ -189,6 +197,14 @@ struct Dec<GQ_Q5_K> {
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16lo(dd[0]); d1 = f16lo(dd[1]); }
     GQ_HD void corr(uint32_t (&a)[2][4], float (&f)[2][2]) const { k4_corr(t, sc, mn, dd, a, f); }
+    // for the dequantise-to-fp16 path: integer weight of run R = fragment value - offs<R>();  w = that * (scale * d) - minterm
+    static constexpr bool HAS_MIN = true;
+    template <int R> static constexpr float offs() { return ((R >> 1) & 1) ? 64.0f : 1024.0f; }
+    template <int G>
+    GQ_HD void minterm(float &m0, float &m1) const {
+        m0 = f16hi(dd[0]) * byte_f32<(G & 3)>(mn[0][G >> 2]);
+        m1 = f16hi(dd[1]) * byte_f32<(G & 3)>(mn[1][G >> 2]);
+    }
 };
 
 // ---- Q6_K -----------------------------------------------------------------------------------------
@@ -250,6 +266,8 @@ struct Dec<GQ_Q6_K> {
             f[0][h] = 96.0f * f16bits(dd[h]);
         }
     }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return (((R >> 1) & 3) >> 1) ? 96.0f : 1056.0f; }
 };
 
 // scale of 32-weight block G from a row's eight fp16 d's
@@ -300,6 +318,8 @@ struct Dec<GQ_Q8_0> {
     GQ_HD void scale(float &s0, float &s1) const { d8_scale<G>(d8, s0, s1); }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 1.0f; d1 = 1.0f; }
     GQ_HD void corr(uint32_t (&a)[1][4], float (&f)[1][2]) const { d8_corr(t, d8, 1152.0f, a, f); }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 1152.0f; }
 };
 
 // ---- Q4_0 (18-byte blocks: d, 16 nibble bytes): exact centring, no correction ------------------------
@@ -330,6 +350,8 @@ struct Dec<GQ_Q4_0> {
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const { d8_scale<G>(d8, s0, s1); }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 1.0f; d1 = 1.0f; }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 0.0f; }
 };
 
 // ---- IQ4_NL (18-byte blocks: d, 16 codebook-index nibble bytes) --------------------------------------
@@ -363,6 +385,8 @@ struct Dec<GQ_IQ4_NL> {
     GQ_HD void scale(float &s0, float &s1) const { d8_scale<G>(d8, s0, s1); }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 1.0f; d1 = 1.0f; }
     GQ_HD void corr(uint32_t (&a)[1][4], float (&f)[1][2]) const { d8_corr(t, d8, 1152.0f, a, f); }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 1152.0f; }
 };
 
 // ---- Q5_0 (22-byte blocks: d, qh u32, 16 nibble bytes): exact centring, no correction -----------------
@@ -405,6 +429,8 @@ struct Dec<GQ_Q5_0> {
     template <int G>
     GQ_HD void scale(float &s0, float &s1) const { d8_scale<G>(d8, s0, s1); }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 1.0f; d1 = 1.0f; }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 0.0f; }
 };
 
 // ---- IQ4_XS ---------------------------------------------------------------------------------------
@@ -466,6 +492,8 @@ struct Dec<GQ_IQ4_XS> {
             f[0][h] = 1152.0f * f16lo(dd[h]);
         }
     }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 1152.0f; }
 };
 
 // multipliers bias/16 of the four runs 4t..4t+3 of the 2-bit types: t even -> bit pairs 0,1 (bias 1024, 256),
@@ -533,6 +561,13 @@ struct Dec<GQ_Q2_K> {
             f[1][h] = f16hi(dd[h]);
         }
     }
+    static constexpr bool HAS_MIN = true;
+    template <int R> static constexpr float offs() { return float(1024 >> (2 * ((R >> 1) & 3))); }
+    template <int G>
+    GQ_HD void minterm(float &m0, float &m1) const {
+        m0 = f16hi(dd[0]) * byte_f32<(G & 3)>(w4(mn[0], G >> 2));
+        m1 = f16hi(dd[1]) * byte_f32<(G & 3)>(w4(mn[1], G >> 2));
+    }
 };
 
 // ---- Q3_K -----------------------------------------------------------------------------------------
@@ -597,6 +632,8 @@ struct Dec<GQ_Q3_K> {
             f[1][h] = 4.0f * d;
         }
     }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return float((1024 >> (2 * ((R >> 1) & 3))) + 4); }
 };
 
 // ---- IQ3_S ----------------------------------------------------------------------------------------
@@ -656,6 +693,8 @@ struct Dec<GQ_IQ3_S> {
         s1 = u32_as_f32(prmt((G & 1) ? sco[1] : sce[1], 0x4B800000u, sel)) - 16777215.0f;
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16bits(dd[0]); d1 = f16bits(dd[1]); }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 0.0f; }
 };
 
 }  // namespace gq

@@ -43,6 +43,42 @@ def _graph_time(fn, n: int, reps: int = 7) -> float:
     return float(np.median(ts)) / n
 
 
+def prefill_main(a, dev) -> None:
+    """Grouped gate_up (K 5120, N 2 x 17408) and down (K 17408, N 5120) at prefill batch sizes: milliseconds and
+    TFLOP/s (2 M K N; dequantisation not counted), the whole call (activation layout + the tcgen05 kernel)."""
+    shapes = {"gate_up": ([17408, 17408], 5120), "down": ([5120], 17408), "q": ([5120], 5120)}
+    for tn in a.types:
+        t = F.TYPE_IDS[tn]
+        for sn in [s for s in a.shapes if s in shapes] or ["gate_up", "down"]:
+            n_outs, k = shapes[sn]
+            tiles = [ops.repack_tiles(synth.random_blocks(n, k, t, seed=i, device=dev), n, t) for i, n in enumerate(n_outs)]
+            packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer(tiles, n_outs, [t] * len(n_outs))
+            del tiles
+            d1 = descs[splits.index(1)]
+            n_total = sum(n_outs)
+            for m in a.m:
+                x = synth.activations(m, k, device=dev)
+                y = torch.empty((m, n_total), dtype=torch.bfloat16, device=dev)
+                for _ in range(2):
+                    ops.prefill_gemm(x, packed, d1, n_total, out=y)
+                torch.cuda.synchronize()
+                if a.eager:
+                    print(f"{tn:7} {sn:8} M={m}: eager", flush=True)
+                    continue
+                ts = []
+                for _ in range(5):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    ops.prefill_gemm(x, packed, d1, n_total, out=y)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1))
+                ms = float(np.median(ts))
+                print(f"{tn:7} {sn:8} K={k} N={n_total} M={m:5}: {ms:8.3f} ms  {2.0 * m * k * n_total / ms / 1e9:7.1f} TFLOP/s", flush=True)
+            del packed, views, descs
+            torch.cuda.empty_cache()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--types", nargs="*", default=list(F.TYPE_IDS))
@@ -50,11 +86,14 @@ def main() -> None:
     ap.add_argument("--m", nargs="*", type=int, default=[1, 8])
     ap.add_argument("--split", nargs="*", type=int, default=[])
     ap.add_argument("--copies-mb", type=float, default=600.0)
+    ap.add_argument("--prefill", action="store_true", help="time the large-batch tcgen05 path on gate_up / down (TFLOP/s)")
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     L = _lib.lib()
+    if a.prefill:
+        return prefill_main(a, dev)
     for tn in a.types:
         t = F.TYPE_IDS[tn]
         for sn in a.shapes:

@@ -187,12 +187,37 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
     return out
 
 
+def prefill_gemm(x: torch.Tensor, packed: torch.Tensor, desc1: torch.Tensor, n_total: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The large-batch path (tcgen05 dequant-GEMM): x bf16 [M, K] -> out bf16 [M, n_total]; desc1 is the run's
+    split-1 descriptor table."""
+    _need_cuda(x, "x")
+    if x.dtype != torch.bfloat16 or x.dim() != 2:
+        raise GqError(f"x must be bf16 [M, K], got {x.dtype} {tuple(x.shape)}")
+    m, k = int(x.shape[0]), int(x.shape[1])
+    if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty((m, n_total), dtype=torch.bfloat16, device=x.device)
+    elif out.dtype != torch.bfloat16 or out.shape != (m, n_total) or (m > 0 and out.stride(1) != 1):
+        raise GqError("out must be bf16 [M, n_total] with unit column stride")
+    if m == 0 or n_total == 0:
+        return out
+    L = lib()
+    ws_bytes = check(L.gq_prefill_workspace_bytes(m, k), "gq_prefill_workspace_bytes")
+    ws = torch.empty(ws_bytes + 1024, dtype=torch.uint8, device=x.device)
+    base = (ws.data_ptr() + 1023) // 1024 * 1024
+    with torch.cuda.device(x.device):
+        check(L.gq_gemm_prefill(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc1.data_ptr(), int(desc1.shape[0]), out.data_ptr(),
+                                out.stride(0), n_total, base, ws_bytes, _stream_ptr(x)), "gq_gemm_prefill")
+    return out
+
+
 def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[torch.Tensor], desc_splits: list[int],
                           tiles: list[torch.Tensor], n_outs: list[int], weight_types: list[int], nb: int, block_bytes: int) -> torch.Tensor:
     """A layer's run of shards in one call: x bf16 [M, K] -> [M, sum(n_outs)] (reference:
     gluon_mul_mat_tiles_grouped, gguf-plugin/gluon/interface.py:141-188).  The row-count dispatch lives
     here, inside the op: up to 64 rows one grouped launch at the split of the table for that row count;
-    above, 64-row blocks of the same kernel at split 1 (the weights stream once per block)."""
+    above, the tcgen05 dequant-GEMM (weights dequantised into shared memory once per 256 batch rows)."""
     m = int(x.shape[0])
     n_total = sum(int(n) for n in n_outs)
     out = torch.empty((m, n_total), dtype=x.dtype, device=x.device)
@@ -205,10 +230,7 @@ def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[tor
             s = 1
         grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, out=out)
         return out
-    d1 = descs[desc_splits.index(1)]
-    for r0 in range(0, m, GEMV_MAX_ROWS):
-        r1 = min(m, r0 + GEMV_MAX_ROWS)
-        grouped_gemm(x[r0:r1], packed, d1, 1, weight_types, n_total, out=out[r0:r1])
+    prefill_gemm(x, packed, descs[desc_splits.index(1)], n_total, out=out)
     return out
 
 

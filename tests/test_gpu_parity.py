@@ -272,3 +272,63 @@ def test_tensor_parallel_shards_sum_to_the_full_result_on_one_gpu():
                 total += lin.finalize()(xp).float().cpu().numpy()
             assert oracle.rel_err(np.concatenate(cols, axis=1), full) < TOL_TIGHT
             assert oracle.rel_err(total, full) < TOL          # eight bf16-rounded partial sums
+
+
+@pytest.mark.parametrize("t", sorted(F.SUPPORTED_TYPES))
+def test_prefill_tcgen05_all_types(t):
+    """The large-batch path (dequantise to shared memory, tcgen05 MMA, accumulator in tensor memory) against the
+    fp64 oracle: odd tile counts (70 rows: the second tile has 6 valid rows; 320 rows: five tiles, the last pair
+    is half empty), batch sizes either side of the 128- and 256-row tiles."""
+    for n_out, k in [(70, 768), (320, 1024)]:
+        raw = synth.random_blocks(n_out, k, t, seed=11 + t)
+        tiles = ops.repack_tiles(raw.to(dev()), n_out, t)
+        d1 = torch.from_numpy(ops.build_descs([t], [n_out], k, 1)).to(dev())
+        for m in (65, 128, 129, 257, 600):
+            x = synth.activations(m, k, device=dev())
+            wide = torch.full((m, n_out + 16), float("nan"), dtype=torch.bfloat16, device=dev())
+            ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out, out=wide[:, 8:8 + n_out])
+            assert torch.isnan(wide[:, :8]).all() and torch.isnan(wide[:, 8 + n_out:]).all()
+            y = wide[:, 8:8 + n_out]
+            assert not torch.isnan(y).any()
+            assert torch.equal(y, ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out)), "not deterministic"
+            err = oracle.rel_err(y.float().cpu().numpy(), ref_gemm(x, raw, t))
+            assert err < TOL_TIGHT, f"{F.TYPE_NAMES[t]} [{n_out}x{k}] M={m}: {err:.3e}"
+
+
+def test_prefill_mixed_run_and_dispatch_boundary():
+    """A mixed-type fused layer through the op at M = 64 (grouped kernel) and M = 65 (tcgen05 path): both within
+    tolerance of the oracle, and per shard bit-identical to the shard alone on the same path."""
+    k = 1024
+    parts = [(192, F.Q4_K), (70, F.IQ3_S), (64, F.Q6_K), (130, F.Q2_K)]
+    raws = [synth.random_blocks(n, k, t, seed=41 + i) for i, (n, t) in enumerate(parts)]
+    tiles = [ops.repack_tiles(r.to(dev()), n, t) for r, (n, t) in zip(raws, parts)]
+    n_outs, wts = [n for n, _ in parts], [t for _, t in parts]
+    packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer(tiles, n_outs, wts)
+    for m in (64, 65, 300):
+        x = synth.activations(m, k, device=dev())
+        y = ops.fused_mul_mat_gguf_tiles_grouped(x, packed, descs, splits, views, n_outs, wts, nb, bb)
+        ref = np.concatenate([ref_gemm(x, r, t) for r, (_, t) in zip(raws, parts)], axis=1)
+        assert oracle.rel_err(y.float().cpu().numpy(), ref) < TOL_TIGHT
+        if m > 64:
+            col = 0
+            for (n, t), tl in zip(parts, tiles):
+                d1 = torch.from_numpy(ops.build_descs([t], [n], k, 1)).to(dev())
+                assert torch.equal(y[:, col:col + n], ops.prefill_gemm(x, tl.reshape(-1), d1, n))
+                col += n
+
+
+def test_prefill_full_size_down_projection_properties():
+    """BASELINE configs[2] shape (down: K 17408, N 5120, Q6_K) at M = 2048: a row/column subset against the
+    oracle and linearity in x at full size."""
+    t, n_out, k, m = F.Q6_K, 5120, 17408, 2048
+    raw = synth.random_blocks(n_out, k, t, seed=14006, device=dev())
+    tiles = ops.repack_tiles(raw, n_out, t)
+    d1 = torch.from_numpy(ops.build_descs([t], [n_out], k, 1)).to(dev())
+    x = synth.activations(m, k, device=dev())
+    y = ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out).float()
+    rows = torch.arange(0, n_out, 41, device=dev())
+    cols_m = np.arange(0, m, 97)
+    ref = ref_gemm(x[cols_m].cpu(), raw[rows].cpu(), t)
+    assert oracle.rel_err(y[cols_m][:, rows].cpu().numpy(), ref) < TOL_TIGHT
+    y2 = ops.prefill_gemm((2 * x.float()).to(torch.bfloat16), tiles.reshape(-1), d1, n_out).float()
+    assert float((y2 - 2 * y).abs().max()) <= 2 ** -7 * float(y.abs().max())
