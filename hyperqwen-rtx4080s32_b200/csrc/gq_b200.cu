@@ -723,6 +723,39 @@ extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t 
                                   workspace_bytes, stream, 7);
 }
 
+// ---- the same call for callers that cannot allocate device memory -------------------------------------
+// Scratch lives in this fixed array, part of the library's device image: every GPU that loads the library
+// holds it until the process exits.  All calls of gq_gemv_grouped_static on a device share it.
+#define GQ_STATIC_WS_BYTES (8ll << 20)
+static __device__ __align__(256) unsigned char g_static_ws[GQ_STATIC_WS_BYTES];
+
+extern "C" int64_t gq_static_workspace_limit(void) { return GQ_STATIC_WS_BYTES; }
+
+extern "C" int gq_gemv_grouped_static(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                                      int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *stream) {
+    if (M < 0 || M > GQ_MAX_GEMV_ROWS || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0 || split < 1) return GQ_ERR_SHAPE;
+    const int64_t need = ws_layout(M, K, n_total, split, nullptr, nullptr);
+    if (need > GQ_STATIC_WS_BYTES) {
+        snprintf(g_cuda_err, sizeof g_cuda_err, "gq_gemv_grouped_static: this call needs %lld bytes of scratch, the built-in buffer holds %lld",
+                 (long long)need, (long long)GQ_STATIC_WS_BYTES);
+        return GQ_ERR_LIMIT;
+    }
+    // In host code `g_static_ws` is only a handle for the symbol; the address the kernels may use is looked up
+    // once per device, with that device current.
+    static void *dev_ptr[64] = {nullptr};
+    int dev = 0;
+    GQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return GQ_ERR_LIMIT;
+    void *ws = dev_ptr[dev];
+    if (!ws) {
+        GQ_CUDA(cudaGetSymbolAddress(&ws, g_static_ws));
+        if (!ws) return GQ_ERR_CUDA;
+        dev_ptr[dev] = ws;
+    }
+    return gq_gemv_grouped_phases(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, ws,
+                                  GQ_STATIC_WS_BYTES, stream, 7);
+}
+
 // ---- prefill ----------------------------------------------------------------------------------------
 static int prefill_nb(int64_t M) { return M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 

@@ -117,6 +117,26 @@ int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, int64_t ldx,
                            int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
                            void *workspace_dev, int64_t workspace_bytes, void *stream, int phases);
 
+/* gq_gemv_grouped without a workspace argument, for callers that cannot allocate device memory at the
+ * point of the call — a plugin op running where the framework's allocator is off limits (inside another
+ * library's callback, under a fixed memory plan, or in a process that handed all of its device memory to a
+ * pool it does not own).  It has no counterpart in the reference, whose launcher always allocates through
+ * torch.  The scratch (prepared activations, split-K partials, the status word) lives in a fixed 8 MiB
+ * buffer built into the library's device image; every GPU that loads the library holds those 8 MiB until the
+ * process exits.  gq_static_workspace_limit() returns that size; a call whose gq_workspace_bytes(M, K,
+ * n_total, split) exceeds it is rejected with GQ_ERR_LIMIT and a message in gq_last_cuda_error, nothing
+ * launched.  The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on a device looks the buffer's address up (a host-side query); make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one buffer, and it keeps the previous call's contents.  The status word
+ *     is cleared at the start of every call; nothing else needs a clean slate.  Two calls whose kernels overlap
+ *     on the GPU (different streams, no ordering between them) race on the buffer: keep them on one stream
+ *     or order them with events.
+ * Arguments and results are those of gq_gemv_grouped. */
+int64_t gq_static_workspace_limit(void);
+int gq_gemv_grouped_static(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                           int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *stream);
+
 /* Workspace bytes of gq_gemm_prefill for a batch of M rows (activations re-laid out for the tensor-core
  * operand, row scales, status). */
 int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K);
