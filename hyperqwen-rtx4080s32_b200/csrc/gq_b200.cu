@@ -294,6 +294,7 @@ struct GemvParams {
     int64_t ldy, n_total;
     int wbytes_max;      // largest tile bytes in the launch (stage stride of the weight buffers)
     int has_iq3s;
+    int cluster;         // 1: the `split` CTAs of a tile form a thread-block cluster and reduce through shared memory
 };
 
 template <int TYPE, int MT, int P>
@@ -448,6 +449,9 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
                 if (++s == stages) { s = 0; ++round; }
             }
         }
+        if (!p.cluster) return;
+        cluster_sync_all();     // the reduction's two cluster barriers need every thread of every CTA
+        cluster_sync_all();
         return;
     }
 
@@ -476,19 +480,41 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
         GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS)
     }
 #undef GQ_CONSUME
-    if (!ok) { if (lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT); return; }
+    if (!ok && lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT);   // the result is then incomplete; the status word says so
 
     // ---- epilogue: rows of the MMA are output columns, columns of the MMA are batch rows ----
     const int g = lane >> 2, t = lane & 3;
+    if (p.cluster) {
+        // split-K inside a cluster: every CTA parks its accumulators in its own shared memory (the stage ring is
+        // idle by now), the CTA of split 0 adds the others' in split order through distributed shared memory and
+        // writes bf16 once.  No partial sums in HBM, no second kernel; the order of the additions is fixed.
+        float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? 4096 : 0));   // its own area: a slower warp may still read the ring
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) red[(warp * MT + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+        cluster_sync_all();
+        if (split_idx == 0) {
+            const uint32_t my = smem_u32(red);
+            for (int s = 1; s < p.split; ++s) {
+                const uint32_t peer = map_to_rank(my, (uint32_t)s);
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt) {
+                    const float4 v = ld_cluster_f4(peer + (uint32_t)(((warp * MT + nt) * 32 + lane) * 16));
+                    acc[nt][0] += v.x; acc[nt][1] += v.y; acc[nt][2] += v.z; acc[nt][3] += v.w;
+                }
+            }
+        }
+        cluster_sync_all();      // peers stay resident until their shared memory has been read
+        if (split_idx != 0) return;
+    }
 #pragma unroll
     for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int r = warp * 16 + g + 8 * (j >> 1);      // row inside the 64-row tile
             const int n = nt * 8 + 2 * t + (j & 1);          // batch row
-            if (r < nvalid && n < p.M) {
+            if (ok && r < nvalid && n < p.M) {
                 const float v = acc[nt][j] * p.ex[n];
-                if (p.split == 1) p.y[(int64_t)n * p.ldy + col0 + r] = __float2bfloat16_rn(v);
+                if (p.split == 1 || p.cluster) p.y[(int64_t)n * p.ldy + col0 + r] = __float2bfloat16_rn(v);
                 else p.partials[((int64_t)split_idx * p.M + n) * p.n_total + col0 + r] = v;
             }
         }
@@ -636,18 +662,28 @@ template <int MT>
 static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream) {
     const int xbytes = 8 * MT * GQ_XROW_BYTES;
     const int stage_bytes = p.wbytes_max + xbytes;
-    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? 4096 : 0);
+    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? 4096 : 0) + (size_t)GQ_CONSUMER_WARPS * MT * 512;
     // opt in once per device to the largest dynamic shared memory any launch of this variant can ask for
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
-        const int max_smem = 4 * (64 * 272 + xbytes) + 4 * 16 + 4096;
+        const int max_smem = 4 * (64 * 272 + xbytes) + 4 * 16 + 4096 + GQ_CONSUMER_WARPS * MT * 512;
         GQ_CUDA(cudaFuncSetAttribute(gemv_grouped_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem > 232448 ? 232448 : max_smem));
         if (dev < 64) done_mask.fetch_or(1ull << dev);
     }
     if (smem > 232448) return GQ_ERR_LIMIT;
-    gemv_grouped_kernel<MT><<<(unsigned)n_desc, 32 * (GQ_CONSUMER_WARPS + 1), smem, stream>>>(p);
+    if (p.cluster) {
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)p.split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.gridDim = dim3((unsigned)n_desc); cfg.blockDim = dim3(32 * (GQ_CONSUMER_WARPS + 1)); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_grouped_kernel<MT>, p));
+    } else {
+        gemv_grouped_kernel<MT><<<(unsigned)n_desc, 32 * (GQ_CONSUMER_WARPS + 1), smem, stream>>>(p);
+    }
     GQ_LAUNCHED();
     return GQ_OK;
 }
@@ -692,11 +728,14 @@ extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, i
     if (maxb < 84 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
     p.wbytes_max = 64 * maxb;   // every stage can hold a tile of any shard of the run
     p.has_iq3s = (run_info >> 16) & 1;
+    // split-K up to 8 reduces inside a thread-block cluster (portable cluster size); larger splits keep the fp32
+    // partials and the separate sum
+    p.cluster = (split > 1 && split <= 8 && n_desc % split == 0) ? 1 : 0;
     const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
     {
         // four stages when four CTAs of them still fit an SM's shared memory, else three
         const int stage_bytes = p.wbytes_max + 8 * mt * GQ_XROW_BYTES;
-        p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? 4096 : 0)) <= 227 * 1024) ? 4 : 3;
+        p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? 4096 : 0) + GQ_CONSUMER_WARPS * mt * 512) <= 227 * 1024) ? 4 : 3;
     }
     int rc = GQ_OK;
     if (phases & 2) {
@@ -708,7 +747,7 @@ extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, i
         }
     }
     if (rc) return rc;
-    if (split > 1 && (phases & 4)) {
+    if (split > 1 && !p.cluster && (phases & 4)) {
         const int64_t n = M * n_total;
         sum_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws.partials, split, M, n_total, (__nv_bfloat16 *)y_dev, ldy);
         GQ_LAUNCHED();
