@@ -169,6 +169,7 @@ def run_ours(args):
     L = _lib.lib()
     st = S.LinearStack(n_layers=args.layers, device=dev, tp_rank=rank, tp_size=world)
     m = args.m
+    st.enable_prefetch(not args.no_l2_prefetch)
     x_dev = st.make_inputs(m)
     x_host = {k: v.cpu().pin_memory() for k, v in x_dev.items()}
     out_host = torch.empty((m, st.hidden), dtype=torch.bfloat16).pin_memory()
@@ -310,7 +311,7 @@ def run_ours(args):
                 "config": {"workload": f"mixed-type {args.layers}-layer GGUF decoder linear stack (BASELINE configs[3]{'/[4] tensor-parallel' if world > 1 else ''}), decode M={m}",
                            "bits_per_weight": round(8 * total_bytes / st.weights_full, 3), "raw_block_bytes": total_bytes,
                            "l2": "weights (10 GB) far exceed L2; no flush needed", "parallelism": f"tp{world}",
-                           "cuda_graph": bool(captured),
+                           "cuda_graph": bool(captured), "l2_prefetch_next_layer": bool(st.prefetch),
                            "weights": "random valid blocks (the reference's test method), seeded"},
                 "tokens_per_s": m / (ms_step * 1e-3),
                 "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
@@ -350,6 +351,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill TFLOP/s leg")
+    ap.add_argument("--no-l2-prefetch", action="store_true", help="do not warm the L2 with the next layer's weights")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

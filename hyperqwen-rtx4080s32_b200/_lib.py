@@ -35,6 +35,7 @@ SIGNATURES = {
     "gq_workspace_bytes": (_i64, [_i64, _i64, _i64, _i32]),
     "gq_gemv_grouped": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _vp]),
     "gq_gemv_grouped_phases": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _vp, _i32]),
+    "gq_gemv_grouped_prefetch": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _vp, _vp, _i64]),
     "gq_static_workspace_limit": (_i64, []),
     "gq_gemv_grouped_static": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp]),
     "gq_prefill_workspace_bytes": (_i64, [_i64, _i64]),

@@ -295,6 +295,8 @@ struct GemvParams {
     int wbytes_max;      // largest tile bytes in the launch (stage stride of the weight buffers)
     int has_iq3s;
     int cluster;         // 1: the `split` CTAs of a tile form a thread-block cluster and reduce through shared memory
+    const uint8_t *pf_ptr;   // weights the caller will multiply next (or null): prefetched into L2 while this launch computes
+    int64_t pf_bytes;
 };
 
 template <int TYPE, int MT, int P>
@@ -447,6 +449,16 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
                 bulk_g2s(st, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + s);
                 bulk_g2s(st + wmax, xsrc + (int64_t)i * abytes, abytes, full + s);
                 if (++s == stages) { s = 0; ++round; }
+            }
+        }
+        else if (p.pf_ptr) {
+            // the producer warp's other lanes: this CTA's share of the next layer's weights, 16 KB per request
+            const int64_t chunk = 16384;
+            const int64_t n_chunks = (p.pf_bytes + chunk - 1) / chunk;
+            for (int64_t c = (int64_t)blockIdx.x * 31 + (lane - 1); c < n_chunks; c += (int64_t)gridDim.x * 31) {
+                const int64_t o = c * chunk;
+                const int64_t sz = (p.pf_bytes - o < chunk ? p.pf_bytes - o : chunk) & ~(int64_t)15;
+                if (sz > 0) prefetch_l2_bulk(p.pf_ptr + o, (uint32_t)sz);
             }
         }
         if (!p.cluster) return;
@@ -700,9 +712,9 @@ extern "C" int gq_run_info(int n_shards, const int32_t *types) {
     return maxb | (iq3s << 16);
 }
 
-extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
-                                      int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
-                                      void *workspace_dev, int64_t workspace_bytes, void *stream, int phases) {
+static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                             int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
+                             int64_t workspace_bytes, void *stream, int phases, const void *next_packed_dev, int64_t next_bytes) {
     if (M < 0 || M > GQ_MAX_GEMV_ROWS || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0 || split < 1) return GQ_ERR_SHAPE;
     if (M == 0 || n_total == 0 || n_desc == 0) return GQ_OK;
     if (!x_dev || !packed_dev || !desc_dev || !y_dev || !workspace_dev) return GQ_ERR_ARG;
@@ -731,6 +743,8 @@ extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, i
     // split-K up to 8 reduces inside a thread-block cluster (portable cluster size); larger splits keep the fp32
     // partials and the separate sum
     p.cluster = (split > 1 && split <= 8 && n_desc % split == 0) ? 1 : 0;
+    p.pf_ptr = (next_packed_dev && next_bytes > 0 && !((uintptr_t)next_packed_dev & 15)) ? (const uint8_t *)next_packed_dev : nullptr;
+    p.pf_bytes = next_bytes;
     const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
     {
         // four stages when four CTAs of them still fit an SM's shared memory, else three
@@ -753,6 +767,21 @@ extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, i
         GQ_LAUNCHED();
     }
     return GQ_OK;
+}
+
+extern "C" int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                                      int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                                      void *workspace_dev, int64_t workspace_bytes, void *stream, int phases) {
+    return gemv_grouped_impl(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
+                             workspace_bytes, stream, phases, nullptr, 0);
+}
+
+extern "C" int gq_gemv_grouped_prefetch(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                                        int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                                        void *workspace_dev, int64_t workspace_bytes, void *stream, const void *next_packed_dev,
+                                        int64_t next_bytes) {
+    return gemv_grouped_impl(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
+                             workspace_bytes, stream, 7, next_packed_dev, next_bytes);
 }
 
 extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,

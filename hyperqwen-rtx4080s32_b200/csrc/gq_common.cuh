@@ -62,6 +62,11 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
                  : "memory");
 }
 
+// ask the L2 to fetch `bytes` (a multiple of 16) starting at a 16-byte aligned global address; returns at once
+__device__ __forceinline__ void prefetch_l2_bulk(const void *gptr, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
+}
+
 // ---- thread-block cluster: barrier over all threads of all CTAs of the cluster, and loads from a peer CTA's
 // shared memory (distributed shared memory) ----------------------------------------------------------------
 __device__ __forceinline__ void cluster_sync_all() {

@@ -158,6 +158,25 @@ def prepare_grouped_layer(tiles_list: Sequence[torch.Tensor], n_outs: Sequence[i
 
 # ---- per call ------------------------------------------------------------------------------------
 
+# packed buffer (data_ptr) -> (data_ptr, bytes) of the packed buffer the model multiplies next; filled by
+# register_prefetch_chain at load time.  A launch on the key prefetches the value into L2 while it computes.
+_NEXT_WEIGHTS: dict[int, tuple[int, int]] = {}
+
+
+def register_prefetch_chain(packed_in_call_order: Sequence[torch.Tensor], cyclic: bool = True) -> None:
+    """Tell the op in which order a model's packed runs are multiplied (qkv, o, gate_up, down, next block ...),
+    so each small-batch launch can warm the L2 with its successor's weights."""
+    bufs = list(packed_in_call_order)
+    for i, b in enumerate(bufs):
+        if i + 1 < len(bufs) or cyclic:
+            nxt = bufs[(i + 1) % len(bufs)]
+            _NEXT_WEIGHTS[b.data_ptr()] = (nxt.data_ptr(), nxt.numel())
+
+
+def clear_prefetch_chain() -> None:
+    _NEXT_WEIGHTS.clear()
+
+
 def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, split: int, wtypes: Sequence[int], n_total: int,
                  out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, phases: int = 7) -> torch.Tensor:
     """One grouped launch for 1..64 rows: x bf16 [M, K] -> out bf16 [M, n_total] (out may be a column view).
@@ -180,6 +199,13 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
     L = lib()
     ws_bytes = check(L.gq_workspace_bytes(m, k, n_total, int(split)), "gq_workspace_bytes")
     ws = workspace if workspace is not None else torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    nxt = _NEXT_WEIGHTS.get(packed.data_ptr()) if phases == 7 else None
+    if nxt is not None:
+        with torch.cuda.device(x.device):
+            check(L.gq_gemv_grouped_prefetch(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc.data_ptr(), int(desc.shape[0]), int(split),
+                                             run_info(wtypes), out.data_ptr(), out.stride(0), n_total, ws.data_ptr(), ws.numel(), _stream_ptr(x),
+                                             nxt[0], min(nxt[1], 96 << 20)), "gq_gemv_grouped_prefetch")
+        return out
     with torch.cuda.device(x.device):
         check(L.gq_gemv_grouped_phases(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc.data_ptr(), int(desc.shape[0]), int(split),
                                        run_info(wtypes), out.data_ptr(), out.stride(0), n_total, ws.data_ptr(), ws.numel(), _stream_ptr(x),

@@ -73,6 +73,17 @@ class LinearStack:
             self.layers.append(blk)
         if device != "cpu":
             torch.cuda.empty_cache()
+        self.prefetch = False
+
+    def enable_prefetch(self, on: bool = True) -> None:
+        """Register the call order of the stack's packed runs so each launch warms the L2 for the next one."""
+        from . import ops
+
+        ops.clear_prefetch_chain()
+        if on:
+            order = [blk[name].gguf_groups[next(iter(blk[name].gguf_groups))][0] for blk in self.layers for name in ("qkv", "o", "gate_up", "down")]
+            ops.register_prefetch_chain(order)
+        self.prefetch = on
 
     def input_sizes(self) -> dict[str, int]:
         blk = self.layers[0]

@@ -117,6 +117,16 @@ int gq_gemv_grouped_phases(const void *x_dev, int64_t M, int64_t K, int64_t ldx,
                            int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
                            void *workspace_dev, int64_t workspace_bytes, void *stream, int phases);
 
+/* gq_gemv_grouped plus a hint: next_packed_dev / next_bytes name the packed weights the caller will multiply
+ * next (the following layer).  While this launch computes, idle lanes of its copy warps ask the L2 (126 MB on
+ * B200) to fetch them, so the next launch starts on L2 hits instead of a cold DRAM burst.  A null pointer or
+ * zero bytes means no hint; the result is the same either way.
+ * Reference: none — the reference's launches start cold; its Ada card's L2 (64 MB) is smaller than a layer. */
+int gq_gemv_grouped_prefetch(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                             int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                             void *workspace_dev, int64_t workspace_bytes, void *stream, const void *next_packed_dev,
+                             int64_t next_bytes);
+
 /* gq_gemv_grouped without a workspace argument, for callers that cannot allocate device memory at the
  * point of the call — a plugin op running where the framework's allocator is off limits (inside another
  * library's callback, under a fixed memory plan, or in a process that handed all of its device memory to a
