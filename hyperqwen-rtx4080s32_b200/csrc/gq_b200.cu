@@ -3,6 +3,7 @@
 // declared in include/gq_b200.h.
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <atomic>
 #include "../../include/gq_b200.h"
 #include "gq_decode.cuh"
@@ -227,6 +228,8 @@ __global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__rest
     __shared__ float red[8];
     __shared__ float s_scale;
     const int m = blockIdx.x;
+    pdl_trigger();    // the grouped kernel behind this one may start fetching weights
+    pdl_wait();       // whatever ran before (possibly still reading this workspace) has finished
     if (m == 0 && threadIdx.x == 0) *status = 0;
     const __nv_bfloat16 *xr = x + (int64_t)m * ldx;
     const int nrun = K >> 4;
@@ -437,17 +440,29 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
     __syncthreads();
 
     if (warp == GQ_CONSUMER_WARPS) {
-        // ---- producer: one thread; per k-block one bulk copy of the weight tile and one of the activation tile ----
+        // ---- producer: one thread; per k-block one bulk copy of the weight tile and one of the activation tile.
+        // The weights do not depend on the kernel in front of this one, so the first stages' weight copies go out
+        // before the dependency wait; the activation tiles (written by the preparation kernel) follow it.  The
+        // kernel behind this one is allowed to start launching when this CTA has two k-blocks left. ----
         if (lane == 0) {
             const uint8_t *src = p.packed + off + (int64_t)kb0 * tile_bytes;
             const uint32_t abytes = (uint32_t)M * GQ_XROW_BYTES;
             const uint8_t *xsrc = p.xt + (int64_t)kb0 * abytes;
-            for (int i = 0, s = 0, round = 0; i < nk; ++i) {
-                if (round > 0 && !mbar_wait(empty + s, (round - 1) & 1)) { atomicExch(p.status, GQ_DEV_TIMEOUT); break; }
+            const int pre = nk < stages ? nk : stages;
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(full + i, (uint32_t)tile_bytes + abytes);
+                bulk_g2s(smem + (size_t)i * stage_bytes, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + i);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) bulk_g2s(smem + (size_t)i * stage_bytes + wmax, xsrc + (int64_t)i * abytes, abytes, full + i);
+            if (nk - pre <= 2) pdl_trigger();
+            for (int i = pre, s = 0, round = 1; i < nk; ++i) {
+                if (!mbar_wait(empty + s, (round - 1) & 1)) { atomicExch(p.status, GQ_DEV_TIMEOUT); break; }
                 uint8_t *st = smem + (size_t)s * stage_bytes;
                 mbar_expect_tx(full + s, (uint32_t)tile_bytes + abytes);
                 bulk_g2s(st, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + s);
                 bulk_g2s(st + wmax, xsrc + (int64_t)i * abytes, abytes, full + s);
+                if (i == nk - 3) pdl_trigger();
                 if (++s == stages) { s = 0; ++round; }
             }
         }
@@ -547,6 +562,13 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const float *__restri
 // ---------------------------------------------------------------------------------------------------
 // C ABI
 // ---------------------------------------------------------------------------------------------------
+// programmatic dependent launch can be switched off for A/B timing (GQ_NO_PDL=1); the kernels are correct either way
+static int use_pdl() {
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("GQ_NO_PDL"); v = (e && e[0] == '1') ? 0 : 1; }
+    return v;
+}
+
 static int ensure_tables() {
     // per-device one-time upload of the two format tables into constant memory
     static std::atomic<unsigned long long> done_mask{0};
@@ -680,21 +702,28 @@ static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream)
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
-        const int max_smem = 4 * (64 * 272 + xbytes) + 4 * 16 + 4096 + GQ_CONSUMER_WARPS * MT * 512;
+        const int max_smem = 8 * (64 * 272 + xbytes) + 8 * 16 + 4096 + GQ_CONSUMER_WARPS * MT * 512;
         GQ_CUDA(cudaFuncSetAttribute(gemv_grouped_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem > 232448 ? 232448 : max_smem));
         if (dev < 64) done_mask.fetch_or(1ull << dev);
     }
     if (smem > 232448) return GQ_ERR_LIMIT;
-    if (p.cluster) {
+    {
         cudaLaunchConfig_t cfg = {};
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)p.split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cudaLaunchAttribute attr[2];
+        int na = 0;
+        if (p.cluster) {
+            attr[na].id = cudaLaunchAttributeClusterDimension;
+            attr[na].val.clusterDim.x = (unsigned)p.split; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1;
+            ++na;
+        }
+        if (use_pdl()) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
         cfg.gridDim = dim3((unsigned)n_desc); cfg.blockDim = dim3(32 * (GQ_CONSUMER_WARPS + 1)); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-        cfg.attrs = attr; cfg.numAttrs = 1;
+        cfg.attrs = attr; cfg.numAttrs = na;
         GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_grouped_kernel<MT>, p));
-    } else {
-        gemv_grouped_kernel<MT><<<(unsigned)n_desc, 32 * (GQ_CONSUMER_WARPS + 1), smem, stream>>>(p);
     }
     GQ_LAUNCHED();
     return GQ_OK;
@@ -727,7 +756,13 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     cudaStream_t st = (cudaStream_t)stream;
 
     if (phases & 1) {
-        prep_x_kernel<<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16 *)x_dev, ldx, (int)K, (int)M, ws.ex, ws.xt, ws.status);
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.gridDim = dim3((unsigned)M); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+        cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
+        GQ_CUDA(cudaLaunchKernelEx(&cfg, prep_x_kernel, (const __nv_bfloat16 *)x_dev, ldx, (int)K, (int)M, ws.ex, ws.xt, ws.status));
         GQ_LAUNCHED();
     }
     if (!(phases & 6)) return GQ_OK;
@@ -747,9 +782,13 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     p.pf_bytes = next_bytes;
     const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
     {
-        // four stages when four CTAs of them still fit an SM's shared memory, else three
+        // ring depth: four stages when four CTAs of them still fit an SM's shared memory, else three (swept on the
+        // 64-layer stack: deeper rings with fewer resident CTAs were slower overall)
         const int stage_bytes = p.wbytes_max + 8 * mt * GQ_XROW_BYTES;
         p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? 4096 : 0) + GQ_CONSUMER_WARPS * mt * 512) <= 227 * 1024) ? 4 : 3;
+        static int forced = -1;   // tuning knob: GQ_STAGES=n overrides the ring depth
+        if (forced < 0) { const char *e = getenv("GQ_STAGES"); forced = e ? atoi(e) : 0; }
+        if (forced >= 2 && forced <= 8) p.stages = forced;
     }
     int rc = GQ_OK;
     if (phases & 2) {

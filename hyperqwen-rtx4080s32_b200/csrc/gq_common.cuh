@@ -67,6 +67,12 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void *gptr, uint32_t byte
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
 }
 
+// ---- programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while
+// its predecessor in the stream still runs; pdl_wait() returns once the predecessor has completed and its
+// writes are visible, pdl_trigger() lets the successor start launching ----------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- thread-block cluster: barrier over all threads of all CTAs of the cluster, and loads from a peer CTA's
 // shared memory (distributed shared memory) ----------------------------------------------------------------
 __device__ __forceinline__ void cluster_sync_all() {
