@@ -863,6 +863,101 @@ extern "C" int gq_gemv_grouped_static(const void *x_dev, int64_t M, int64_t K, i
                                   GQ_STATIC_WS_BYTES, stream, 7);
 }
 
+// ---- small-message all-reduce over peer memory (tensor-parallel row-parallel layers) ---------------------
+// One-shot, push based: every rank stores its bf16 vector into its slot of every peer's buffer (plain stores
+// over NVLink into memory the peers mapped for each other), publishes a per-CTA flag, waits — with a limit —
+// for the peers' flags, and sums the slots from its OWN memory in rank order (deterministic, fp32, one bf16
+// rounding).  No loads from remote memory, no multicast.  Two slot sets alternate by call parity; the call
+// number lives in device memory (one counter per CTA) so a captured CUDA graph replays correctly.
+// The reference has no collective of its own on this path (docs/multi-gpu.md:8-13 leaves it to vLLM's NCCL).
+#define GQ_AR_MAX_WORLD 8
+#define GQ_AR_CTAS 16
+#define GQ_AR_SPIN_LIMIT (1u << 25)
+
+struct ArPeers {
+    uint8_t *buf[GQ_AR_MAX_WORLD];      // data area of each rank's buffer: [2 sets][world][slot_bytes]
+    uint32_t *flags[GQ_AR_MAX_WORLD];   // flag area of each rank's buffer: [2 sets][world][GQ_AR_CTAS]
+};
+
+__global__ void __launch_bounds__(256) allreduce_push_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, int64_t n_vec, int rank,
+                                                             int world, ArPeers peers, int64_t slot_bytes, uint32_t *counters, int *status) {
+    __shared__ uint32_t s_seq;
+    __shared__ int s_fail;
+    const int c = blockIdx.x, G = gridDim.x;
+    if (threadIdx.x == 0) { s_seq = counters[c] + 1; s_fail = 0; }
+    __syncthreads();
+    const uint32_t seq = s_seq, set = seq & 1u;
+    const int64_t per = (n_vec + G - 1) / G, v0 = (int64_t)c * per, v1 = v0 + per < n_vec ? v0 + per : n_vec;
+    // push this CTA's share of the vector into slot `rank` of every rank's buffer (own included)
+    for (int p = 0; p < world; ++p) {
+        uint4 *dst = reinterpret_cast<uint4 *>(peers.buf[p] + ((int64_t)set * world + rank) * slot_bytes);
+        for (int64_t i = v0 + threadIdx.x; i < v1; i += 256) dst[i] = in[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < world) {
+        volatile uint32_t *f = peers.flags[threadIdx.x] + ((int64_t)set * world + rank) * G + c;
+        *f = seq;
+        // wait for rank threadIdx.x's share to have landed here
+        volatile uint32_t *mine = peers.flags[rank] + ((int64_t)set * world + threadIdx.x) * G + c;
+        uint32_t it = 0;
+        while (*mine != seq) {
+            if (++it > GQ_AR_SPIN_LIMIT) { s_fail = 1; break; }
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (threadIdx.x == 0) { atomicExch(status, GQ_DEV_TIMEOUT); counters[c] = seq; }
+        return;
+    }
+    __threadfence_system();
+    const uint8_t *base = peers.buf[rank] + (int64_t)set * world * slot_bytes;
+    for (int64_t i = v0 + threadIdx.x; i < v1; i += 256) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < world; ++r) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(base + (int64_t)r * slot_bytes) + i);
+            const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        }
+        uint4 o;
+        __nv_bfloat162 *ob = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        out[i] = o;
+    }
+    if (threadIdx.x == 0) counters[c] = seq;
+}
+
+extern "C" int64_t gq_allreduce_buffer_bytes(int world, int64_t max_bytes) {
+    if (world < 1 || world > GQ_AR_MAX_WORLD || max_bytes <= 0) return GQ_ERR_ARG;
+    const int64_t slot = align256(max_bytes);
+    // [flags 2*world*CTAS u32 | counters CTAS u32 | status] padded to 4096, then data 2 * world * slot
+    return 4096 + 2 * (int64_t)world * slot;
+}
+
+extern "C" int gq_allreduce_push(const void *in_dev, void *out_dev, int64_t n_bytes, int rank, int world, const uint64_t *peer_buffers,
+                                 int64_t max_bytes, void *stream) {
+    if (world < 1 || world > GQ_AR_MAX_WORLD || rank < 0 || rank >= world) return GQ_ERR_ARG;
+    if (n_bytes < 0 || n_bytes > max_bytes || (n_bytes & 15)) return GQ_ERR_SHAPE;
+    if (n_bytes == 0) return GQ_OK;
+    if (!in_dev || !out_dev || !peer_buffers || ((uintptr_t)in_dev & 15) || ((uintptr_t)out_dev & 15)) return GQ_ERR_ARG;
+    ArPeers peers;
+    for (int p = 0; p < GQ_AR_MAX_WORLD; ++p) { peers.buf[p] = nullptr; peers.flags[p] = nullptr; }
+    for (int p = 0; p < world; ++p) {
+        if (!peer_buffers[p] || (peer_buffers[p] & 255)) return GQ_ERR_ARG;
+        peers.flags[p] = reinterpret_cast<uint32_t *>(peer_buffers[p]);
+        peers.buf[p] = reinterpret_cast<uint8_t *>(peer_buffers[p]) + 4096;
+    }
+    uint8_t *own = reinterpret_cast<uint8_t *>(peer_buffers[rank]);
+    uint32_t *counters = reinterpret_cast<uint32_t *>(own + 2 * GQ_AR_MAX_WORLD * GQ_AR_CTAS * 4);
+    int *status = reinterpret_cast<int *>(own + 2 * GQ_AR_MAX_WORLD * GQ_AR_CTAS * 4 + GQ_AR_CTAS * 4);
+    allreduce_push_kernel<<<GQ_AR_CTAS, 256, 0, (cudaStream_t)stream>>>((const uint4 *)in_dev, (uint4 *)out_dev, n_bytes / 16, rank, world, peers,
+                                                                     align256(max_bytes), counters, status);
+    GQ_LAUNCHED();
+    return GQ_OK;
+}
+
 // ---- prefill ----------------------------------------------------------------------------------------
 static int prefill_nb(int64_t M) { return M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 

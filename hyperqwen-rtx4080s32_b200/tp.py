@@ -64,10 +64,75 @@ def pad_input(x: torch.Tensor, pad: KPad | None) -> torch.Tensor:
     return out
 
 
+class PushAllReduce:
+    """The library's one-shot all-reduce for small bf16 messages (gq_allreduce_push): each rank stores its vector
+    into its slot of every peer's buffer over NVLink, publishes per-CTA flags, waits with a limit for the peers'
+    flags and sums from its own memory in rank order.  Buffers come from torch's symmetric memory (peer-mapped
+    allocations); messages above `max_bytes` go to NCCL."""
+
+    def __init__(self, max_bytes: int = 64 * 5120 * 2, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from ._lib import check, lib
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.max_bytes = int(max_bytes)
+        L = lib()
+        nbytes = check(L.gq_allreduce_buffer_bytes(self.world, self.max_bytes), "gq_allreduce_buffer_bytes")
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.buf.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert len(ptrs) == self.world and ptrs[self.rank] == self.buf.data_ptr()
+        self._ptrs = (ctypes.c_uint64 * self.world)(*ptrs)
+        self._lib = L
+
+    def status(self) -> int:
+        return int(self.buf[2 * 8 * 16 * 4 + 16 * 4:2 * 8 * 16 * 4 + 16 * 4 + 4].view(torch.int32).item())
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        from ._lib import check
+
+        n = t.numel() * t.element_size()
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or n > self.max_bytes or n % 16 or t.data_ptr() % 16:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+            return t
+        check(self._lib.gq_allreduce_push(t.data_ptr(), t.data_ptr(), n, self.rank, self.world, self._ptrs, self.max_bytes,
+                                          torch.cuda.current_stream(t.device).cuda_stream), "gq_allreduce_push")
+        return t
+
+
+_FAST = None
+
+
+def enable_push_all_reduce(max_bytes: int = 64 * 5120 * 2, group=None) -> PushAllReduce:
+    """Route all_reduce_ of small bf16 tensors through the library's kernel (call on every rank, after
+    init_process_group, outside stream capture)."""
+    global _FAST
+    _FAST = PushAllReduce(max_bytes, group)
+    return _FAST
+
+
+def disable_push_all_reduce() -> None:
+    global _FAST
+    _FAST = None
+
+
 def all_reduce_(t: torch.Tensor, group=None) -> torch.Tensor:
-    """Sum of the ranks' partial outputs (NCCL over NVLink on GPUs, gloo on CPU)."""
+    """Sum of the ranks' partial outputs: the library's push all-reduce for small bf16 messages when enabled,
+    else NCCL over NVLink on GPUs (gloo on CPU)."""
     import torch.distributed as dist
 
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        if _FAST is not None and t.is_cuda:
+            return _FAST(t)
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
     return t

@@ -147,6 +147,19 @@ int64_t gq_static_workspace_limit(void);
 int gq_gemv_grouped_static(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
                            int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *stream);
 
+/* Small-message all-reduce (sum, bf16) for the row-parallel layers under tensor parallelism, one process per
+ * GPU.  Every rank owns a buffer of gq_allreduce_buffer_bytes(world, max_bytes) bytes that all ranks have
+ * mapped (peer-accessible: e.g. torch.distributed._symmetric_memory), zeroed once before the first call;
+ * peer_buffers[p] is rank p's buffer as seen from the calling process (host array of `world` addresses).
+ * in_dev / out_dev: bf16, n_bytes a multiple of 16, at most max_bytes (the value the buffers were sized
+ * with); out may alias in.  Every rank must make the same sequence of calls.  The kernel pushes its data
+ * into the peers' buffers with plain stores, waits with a limit for the peers' flags (a timeout sets the
+ * status word at byte 2*8*16*4 + 16*4 of the rank's own buffer) and sums from its own memory in rank order.
+ * Reference: none — the reference leaves the collective to vLLM (docs/multi-gpu.md:8-13). */
+int64_t gq_allreduce_buffer_bytes(int world, int64_t max_bytes);
+int gq_allreduce_push(const void *in_dev, void *out_dev, int64_t n_bytes, int rank, int world, const uint64_t *peer_buffers,
+                      int64_t max_bytes, void *stream);
+
 /* Workspace bytes of gq_gemm_prefill for a batch of M rows (activations re-laid out for the tensor-core
  * operand, row scales, status). */
 int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K);

@@ -332,3 +332,40 @@ def test_prefill_full_size_down_projection_properties():
     assert oracle.rel_err(y[cols_m][:, rows].cpu().numpy(), ref) < TOL_TIGHT
     y2 = ops.prefill_gemm((2 * x.float()).to(torch.bfloat16), tiles.reshape(-1), d1, n_out).float()
     assert float((y2 - 2 * y).abs().max()) <= 2 ** -7 * float(y.abs().max())
+
+
+def test_push_all_reduce_single_rank_degenerate(gq_lib):
+    """The push all-reduce kernel with a world of one (its own buffer is the only peer): the result is the input,
+    the per-CTA call counters advance, the slot sets alternate, and a replayed CUDA graph keeps working.  The
+    multi-rank exchange itself is checked on several GPUs by `python -m hyperqwen_rtx4080s32_b200.tp_check`."""
+    import ctypes
+
+    max_bytes = 64 * 5120 * 2
+    nbytes = gq_lib.gq_allreduce_buffer_bytes(1, max_bytes)
+    assert nbytes == 4096 + 2 * max_bytes
+    buf = torch.zeros(nbytes, dtype=torch.uint8, device=dev())
+    ptrs = (ctypes.c_uint64 * 1)(buf.data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    for m in (1, 8, 64):
+        x = synth.activations(m, 5120, seed=m, device=dev())
+        y = torch.empty_like(x)
+        assert gq_lib.gq_allreduce_push(x.data_ptr(), y.data_ptr(), x.numel() * 2, 0, 1, ptrs, max_bytes, stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(x, y)
+    counters = buf[1024:1024 + 64].view(torch.int32)
+    assert counters.tolist() == [3] * 16 and int(buf[1088:1092].view(torch.int32).item()) == 0
+    x = synth.activations(8, 5120, device=dev())
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            assert gq_lib.gq_allreduce_push(x.data_ptr(), x.data_ptr(), x.numel() * 2, 0, 1, ptrs, max_bytes, s.cuda_stream) == 0
+    torch.cuda.current_stream().wait_stream(s)
+    before = x.clone()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(x, before) and counters.tolist() == [6] * 16
+    assert gq_lib.gq_allreduce_push(x.data_ptr(), x.data_ptr(), max_bytes + 16, 0, 1, ptrs, max_bytes, stream) == -2
+    assert gq_lib.gq_allreduce_push(x.data_ptr(), x.data_ptr(), 32, 1, 1, ptrs, max_bytes, stream) == -3
