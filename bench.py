@@ -166,6 +166,10 @@ def run_ours(args):
         # graph capture of NCCL collectives: the watchdog thread must not touch CUDA while a capture is open
         os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+        if not args.nccl_allreduce:
+            from hyperqwen_rtx4080s32_b200 import tp as _tp
+
+            _tp.enable_push_all_reduce(max_bytes=max(64, args.m) * 5120 * 2)
     L = _lib.lib()
     st = S.LinearStack(n_layers=args.layers, device=dev, tp_rank=rank, tp_size=world)
     m = args.m
@@ -310,7 +314,7 @@ def run_ours(args):
                 "data": "synthetic",
                 "config": {"workload": f"mixed-type {args.layers}-layer GGUF decoder linear stack (BASELINE configs[3]{'/[4] tensor-parallel' if world > 1 else ''}), decode M={m}",
                            "bits_per_weight": round(8 * total_bytes / st.weights_full, 3), "raw_block_bytes": total_bytes,
-                           "l2": "weights (10 GB) far exceed L2; no flush needed", "parallelism": f"tp{world}",
+                           "l2": "weights (10 GB) far exceed L2; no flush needed", "parallelism": f"tp{world}", "all_reduce": ("none" if world == 1 else "nccl" if args.nccl_allreduce else "push kernel over NVLink peer memory (gq_allreduce_push)"),
                            "cuda_graph": bool(captured), "l2_prefetch_next_layer": bool(st.prefetch),
                            "weights": "random valid blocks (the reference's test method), seeded"},
                 "tokens_per_s": m / (ms_step * 1e-3),
@@ -351,6 +355,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill TFLOP/s leg")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: use NCCL for the row-parallel all-reduce instead of the library's push kernel")
     ap.add_argument("--no-l2-prefetch", action="store_true", help="do not warm the L2 with the next layer's weights")
     args = ap.parse_args()
     if args.impl == "reference":

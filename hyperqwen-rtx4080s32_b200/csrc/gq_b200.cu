@@ -893,15 +893,17 @@ __global__ void __launch_bounds__(256) allreduce_push_kernel(const uint4 *__rest
         uint4 *dst = reinterpret_cast<uint4 *>(peers.buf[p] + ((int64_t)set * world + rank) * slot_bytes);
         for (int64_t i = v0 + threadIdx.x; i < v1; i += 256) dst[i] = in[i];
     }
-    __threadfence_system();
     __syncthreads();
     if ((int)threadIdx.x < world) {
-        volatile uint32_t *f = peers.flags[threadIdx.x] + ((int64_t)set * world + rank) * G + c;
-        *f = seq;
-        // wait for rank threadIdx.x's share to have landed here
-        volatile uint32_t *mine = peers.flags[rank] + ((int64_t)set * world + threadIdx.x) * G + c;
-        uint32_t it = 0;
-        while (*mine != seq) {
+        // release at system scope: the stores of this CTA (ordered before by the barrier) are visible to the peer
+        // before the flag is; the matching acquire load on the peer's side orders its reads of the slot after it
+        uint32_t *f = peers.flags[threadIdx.x] + ((int64_t)set * world + rank) * G + c;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+        const uint32_t *mine = peers.flags[rank] + ((int64_t)set * world + threadIdx.x) * G + c;
+        uint32_t it = 0, v;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v == seq) break;
             if (++it > GQ_AR_SPIN_LIMIT) { s_fail = 1; break; }
         }
     }
@@ -910,7 +912,6 @@ __global__ void __launch_bounds__(256) allreduce_push_kernel(const uint4 *__rest
         if (threadIdx.x == 0) { atomicExch(status, GQ_DEV_TIMEOUT); counters[c] = seq; }
         return;
     }
-    __threadfence_system();
     const uint8_t *base = peers.buf[rank] + (int64_t)set * world * slot_bytes;
     for (int64_t i = v0 + threadIdx.x; i < v1; i += 256) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
