@@ -670,18 +670,16 @@ extern "C" int64_t gq_build_descs(int n_shards, const int32_t *types, const int6
 }
 
 extern "C" int gq_split_for(int64_t n_tiles, int64_t nb, int64_t M, int avg_bytes_per_256, int sm_count) {
+    (void)M; (void)avg_bytes_per_256;
     if (n_tiles <= 0 || nb <= 0) return 1;
     if (sm_count <= 0) sm_count = 148;
-    // enough CTAs for about three per SM, each keeping at least two k-blocks, the fp32 partials held to a
-    // sixth of the weight bytes
-    int64_t s = (3 * (int64_t)sm_count + n_tiles - 1) / n_tiles;
-    if (s > nb / 2) s = nb / 2;
-    if (s > 16) s = 16;
-    if (M > 0 && avg_bytes_per_256 > 0) {
-        // partial traffic 2 * S * M * 64 * 4 bytes per tile against nb * 64 * bytes_per_256 of weights
-        const int64_t cap = (nb * avg_bytes_per_256) / (6 * 8 * (M < 8 ? 8 : M));
-        if (s > cap) s = cap;
-    }
+    // from sweeps on B200 (Q4_K / IQ3_S / Q2_K; 80-, 112-, 272- and 544-tile layers at K 5120 and 17408): about five
+    // k-blocks per CTA, no more than ~4.5 CTAs per SM, and at most 8 so the split stays inside one thread-block
+    // cluster (the reduction then needs no partial sums in HBM)
+    int64_t by_ctas = (9 * (int64_t)sm_count / 2) / n_tiles;
+    int64_t by_k = (nb + 2) / 5;
+    int64_t s = by_ctas < by_k ? by_ctas : by_k;
+    if (s > 8) s = 8;
     if (s < 1) s = 1;
     if (s > nb) s = nb;
     return (int)s;
