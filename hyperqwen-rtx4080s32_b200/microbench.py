@@ -97,15 +97,18 @@ def main() -> None:
     for tn in a.types:
         t = F.TYPE_IDS[tn]
         for sn in a.shapes:
-            n_out, k = SHAPES[sn]
+            n_out, k = SHAPES[sn] if sn in SHAPES else tuple(int(v) for v in sn.split("x"))   # a name or "NxK"
             nbytes = F.raw_bytes(t, n_out, k)
-            ncopy = max(2, int(a.copies_mb * 1e6 // nbytes))
+            ncopy = max(2, int(a.copies_mb * 1e6 // nbytes)) if a.copies_mb > 0 else 1
             packs = []
             for c in range(ncopy):
                 raw = synth.random_blocks(n_out, k, t, seed=c, device=dev)
                 packs.append(ops.repack_tiles(raw, n_out, t).reshape(-1))
                 del raw
             nb, n_tiles = k // 256, -(-n_out // 64)
+            if a.copies_mb <= 0:
+                packs = packs * 8        # --copies-mb 0: one copy, replayed eight times per graph (weights stay in L2)
+                ncopy = 8
             for m in a.m:
                 x = synth.activations(m, k, device=dev)
                 auto = ops.grouped_split_for(n_tiles, nb, m=m, block_bytes=F.BYTES_PER_256[t])
