@@ -223,22 +223,79 @@ static int64_t ws_layout(int64_t M, int64_t K, int64_t n_total, int split, void 
     return off;
 }
 
-__global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int K, int M, float *__restrict__ ex,
-                                                     uint8_t *__restrict__ xt, int *status) {
-    __shared__ float red[8];
+#define GQ_PREP_THREADS 512
+#define GQ_PREP_VECS 5      // 16-byte loads a thread keeps in registers: rows up to 512 * 5 * 8 = 20480 activations are read once
+
+__device__ __forceinline__ float amax8(const uint4 &v) {
+    const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&v);
+    float a = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(b[j]);
+        a = fmaxf(a, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+    return a;
+}
+
+// eight activations (half a 16-weight run) -> fp16 at `scale`, stored into the staged tile; the run's fp32 sum is
+// completed with the neighbouring lane, which holds the other half
+__device__ __forceinline__ void prep_store8(const uint4 &v, int64_t vec, float scale, int M, int m, uint8_t *__restrict__ xt) {
+    const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&v);
+    uint4 o;
+    __half2 *oh = reinterpret_cast<__half2 *>(&o);
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(b[j]);
+        oh[j] = __floats2half2_rn(f.x * scale, f.y * scale);
+        sum += __low2float(oh[j]) + __high2float(oh[j]);
+    }
+    const int64_t k = vec * 8;                       // first activation of this vector
+    const int kb = (int)(k >> 8), rr = (int)((k >> 4) & 15);
+    uint8_t *row = xt + ((int64_t)kb * M + m) * GQ_XROW_BYTES;
+    *reinterpret_cast<uint4 *>(row + (k & 255) * 2) = o;
+    // the two halves of a run sit in lanes 2i and 2i+1: the same order of additions as one pass over the run
+    const float other = __shfl_xor_sync(0xffffffffu, sum, 1);
+    if (!(vec & 1)) {
+        const float tot = sum + other;
+        const __half hi = __float2half_rn(tot);
+        const __half lo = __float2half_rn(tot - __half2float(hi));
+        __half *so = reinterpret_cast<__half *>(row + GQ_XROW_SX);
+        so[rr] = hi;
+        so[16 + rr] = lo;
+    }
+}
+
+__global__ void __launch_bounds__(GQ_PREP_THREADS) prep_x_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int K, int M,
+                                                                 float *__restrict__ ex, uint8_t *__restrict__ xt, int *status) {
+    __shared__ float red[GQ_PREP_THREADS / 32];
     __shared__ float s_scale;
     const int m = blockIdx.x;
     pdl_trigger();    // the grouped kernel behind this one may start fetching weights
     pdl_wait();       // whatever ran before (possibly still reading this workspace) has finished
     if (m == 0 && threadIdx.x == 0) *status = 0;
     const __nv_bfloat16 *xr = x + (int64_t)m * ldx;
-    const int nrun = K >> 4;
+    const int nvec = K >> 3;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);      // 16-byte loads need an aligned row
+    uint4 v[GQ_PREP_VECS];
     float amax = 0.0f;
-    for (int r = threadIdx.x; r < nrun; r += 256) {
+    if (vec_ok) {
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(xr + 16 * r + j));
-            amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+        for (int i = 0; i < GQ_PREP_VECS; ++i) {
+            const int idx = threadIdx.x + i * GQ_PREP_THREADS;
+            v[i] = idx < nvec ? __ldg(reinterpret_cast<const uint4 *>(xr) + idx) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int i = 0; i < GQ_PREP_VECS; ++i) amax = fmaxf(amax, amax8(v[i]));
+        for (int idx = threadIdx.x + GQ_PREP_VECS * GQ_PREP_THREADS; idx < nvec; idx += GQ_PREP_THREADS)
+            amax = fmaxf(amax, amax8(__ldg(reinterpret_cast<const uint4 *>(xr) + idx)));
+    } else {
+        for (int idx = threadIdx.x; idx < nvec; idx += GQ_PREP_THREADS) {
+            uint4 t;
+            uint32_t *tw = reinterpret_cast<uint32_t *>(&t);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tw[j] = *reinterpret_cast<const uint32_t *>(xr + 8 * idx + 2 * j);
+            amax = fmaxf(amax, amax8(t));
         }
     }
 #pragma unroll
@@ -247,7 +304,7 @@ __global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__rest
     __syncthreads();
     if (threadIdx.x == 0) {
         float a = red[0];
-        for (int i = 1; i < 8; ++i) a = fmaxf(a, red[i]);
+        for (int i = 1; i < GQ_PREP_THREADS / 32; ++i) a = fmaxf(a, red[i]);
         // scale = 2^(9 - e), amax * scale in [512, 1024); identity for a zero, tiny or non-finite row
         int e = 9;
         if (a > 0.0f && a < 3.0e38f) { e = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127; if (e < -100) e = -100; }
@@ -256,23 +313,23 @@ __global__ void __launch_bounds__(256) prep_x_kernel(const __nv_bfloat16 *__rest
     }
     __syncthreads();
     const float scale = s_scale;
-    for (int r = threadIdx.x; r < nrun; r += 256) {
-        const int kb = r >> 4, rr = r & 15;
-        uint8_t *row = xt + ((int64_t)kb * M + m) * GQ_XROW_BYTES;
-        __half *xo = reinterpret_cast<__half *>(row) + 16 * rr;
-        float sum = 0.0f;
+    // nvec is a multiple of 32 (K of 256), so whole warps run every iteration and the lane-pair exchange is safe
+    if (vec_ok) {
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(xr + 16 * r + j));
-            const __half2 h = __floats2half2_rn(v.x * scale, v.y * scale);
-            *reinterpret_cast<__half2 *>(xo + j) = h;
-            sum += __low2float(h) + __high2float(h);
+        for (int i = 0; i < GQ_PREP_VECS; ++i) {
+            const int idx = threadIdx.x + i * GQ_PREP_THREADS;
+            if (idx < nvec) prep_store8(v[i], idx, scale, M, m, xt);
         }
-        const __half hi = __float2half_rn(sum);
-        const __half lo = __float2half_rn(sum - __half2float(hi));
-        __half *so = reinterpret_cast<__half *>(row + GQ_XROW_SX);
-        so[rr] = hi;
-        so[16 + rr] = lo;
+        for (int idx = threadIdx.x + GQ_PREP_VECS * GQ_PREP_THREADS; idx < nvec; idx += GQ_PREP_THREADS)
+            prep_store8(__ldg(reinterpret_cast<const uint4 *>(xr) + idx), idx, scale, M, m, xt);
+    } else {
+        for (int idx = threadIdx.x; idx < nvec; idx += GQ_PREP_THREADS) {
+            uint4 t;
+            uint32_t *tw = reinterpret_cast<uint32_t *>(&t);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tw[j] = *reinterpret_cast<const uint32_t *>(xr + 8 * idx + 2 * j);
+            prep_store8(t, idx, scale, M, m, xt);
+        }
     }
 }
 
@@ -758,7 +815,7 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.gridDim = dim3((unsigned)M); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+        cfg.gridDim = dim3((unsigned)M); cfg.blockDim = dim3(GQ_PREP_THREADS); cfg.dynamicSmemBytes = 0; cfg.stream = st;
         cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
         GQ_CUDA(cudaLaunchKernelEx(&cfg, prep_x_kernel, (const __nv_bfloat16 *)x_dev, ldx, (int)K, (int)M, ws.ex, ws.xt, ws.status));
         GQ_LAUNCHED();
