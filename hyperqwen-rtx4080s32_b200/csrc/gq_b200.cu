@@ -462,8 +462,13 @@ __device__ __forceinline__ bool consume(const uint8_t *smem, uint64_t *full, uin
     return true;
 }
 
-template <int MT>
-__global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_kernel(const GemvParams p) {
+// MINB = CTAs per SM the compiler must leave room for (0: its own choice).  For the M <= 8 form 4 gives it 96
+// registers, which it turns into more loads and MMAs in flight per warp: measured 14 % faster than the 72-register
+// build when a CTA walks ten or more k-blocks, a little slower on launches of many short CTAs, 2 % faster on the
+// mixed stack.  (Compiling both and choosing per call was slower than either alone: alternating between two large
+// kernels costs more in instruction-cache misses at every launch than the better fit gains.)
+template <int MT, int MINB>
+__global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_grouped_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: [stages x (weights wbytes_max | activation tile)] [full barriers] [empty barriers] [IQ3_S grid]
     const int stages = p.stages, wmax = p.wbytes_max, M = p.M;
@@ -486,13 +491,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
         fence_barrier_init();
     }
     if (p.has_iq3s && type == GQ_IQ3_S) {
-        for (int i = threadIdx.x; i < 512; i += blockDim.x) {
-            const uint32_t w = c_iq3s_grid[i];
-            uint2 e;
-            e.x = h2_as_u32(__floats2half2_rn((float)(w & 0xFF), (float)((w >> 8) & 0xFF)));
-            e.y = h2_as_u32(__floats2half2_rn((float)((w >> 16) & 0xFF), (float)(w >> 24)));
-            grid_s[i] = e;
-        }
+        for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]);
     }
     __syncthreads();
 
@@ -572,7 +571,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1)) gemv_grouped_ker
         // split-K inside a cluster: every CTA parks its accumulators in its own shared memory (the stage ring is
         // idle by now), the CTA of split 0 adds the others' in split order through distributed shared memory and
         // writes bf16 once.  No partial sums in HBM, no second kernel; the order of the additions is fixed.
-        float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? 4096 : 0));   // its own area: a slower warp may still read the ring
+        float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0));   // its own area: a slower warp may still read the ring
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt) red[(warp * MT + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
         cluster_sync_all();
@@ -730,14 +729,16 @@ extern "C" int gq_split_for(int64_t n_tiles, int64_t nb, int64_t M, int avg_byte
     (void)M; (void)avg_bytes_per_256;
     if (n_tiles <= 0 || nb <= 0) return 1;
     if (sm_count <= 0) sm_count = 148;
-    // from sweeps on B200 (Q4_K / IQ3_S / Q2_K; 80-, 112-, 272- and 544-tile layers at K 5120 and 17408): about five
-    // k-blocks per CTA, no more than ~4.5 CTAs per SM, and at most 8 so the split stays inside one thread-block
-    // cluster (the reduction then needs no partial sums in HBM)
-    int64_t by_ctas = (9 * (int64_t)sm_count / 2) / n_tiles;
-    int64_t by_k = (nb + 2) / 5;
-    int64_t s = by_ctas < by_k ? by_ctas : by_k;
-    if (s > 8) s = 8;
-    if (s < 1) s = 1;
+    // from sweeps on B200 (Q4_K / Q2_K / IQ3_S / IQ4_XS; 80-, 112-, 272- and 544-tile layers at K 5120 and 17408): the
+    // largest split that (a) leaves a CTA at least three k-blocks, (b) stays inside one thread-block cluster (8), and
+    // (c) keeps the launch in one wave of four CTAs per SM — counting that clusters cannot use every slot: a launch
+    // of clusters of S fills at most about 1 - 0.03 (S - 1) of them before a second wave starts
+    const int64_t slots = 4 * (int64_t)sm_count;
+    int64_t s_max = nb / 3;
+    if (s_max > 8) s_max = 8;
+    int64_t s = 1;
+    for (int64_t c = 2; c <= s_max; ++c)
+        if (c * n_tiles * 100 <= slots * (100 - 3 * (c - 1))) s = c;
     if (s > nb) s = nb;
     return (int)s;
 }
@@ -747,18 +748,18 @@ extern "C" int64_t gq_workspace_bytes(int64_t M, int64_t K, int64_t n_total, int
     return ws_layout(M, K, n_total, split, nullptr, nullptr);
 }
 
-template <int MT>
+template <int MT, int MINB>
 static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream) {
     const int xbytes = 8 * MT * GQ_XROW_BYTES;
     const int stage_bytes = p.wbytes_max + xbytes;
-    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? 4096 : 0) + (size_t)GQ_CONSUMER_WARPS * MT * 512;
+    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) + (size_t)GQ_CONSUMER_WARPS * MT * 512;
     // opt in once per device to the largest dynamic shared memory any launch of this variant can ask for
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
-        const int max_smem = 8 * (64 * 272 + xbytes) + 8 * 16 + 4096 + GQ_CONSUMER_WARPS * MT * 512;
-        GQ_CUDA(cudaFuncSetAttribute(gemv_grouped_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem > 232448 ? 232448 : max_smem));
+        const int max_smem = 8 * (64 * 272 + xbytes) + 8 * 16 + GQ_IQ3S_SMEM_BYTES + GQ_CONSUMER_WARPS * MT * 512;
+        GQ_CUDA(cudaFuncSetAttribute(gemv_grouped_kernel<MT, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem > 232448 ? 232448 : max_smem));
         if (dev < 64) done_mask.fetch_or(1ull << dev);
     }
     if (smem > 232448) return GQ_ERR_LIMIT;
@@ -778,7 +779,7 @@ static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream)
         }
         cfg.gridDim = dim3((unsigned)n_desc); cfg.blockDim = dim3(32 * (GQ_CONSUMER_WARPS + 1)); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
         cfg.attrs = attr; cfg.numAttrs = na;
-        GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_grouped_kernel<MT>, p));
+        GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_grouped_kernel<MT, MINB>, p));
     }
     GQ_LAUNCHED();
     return GQ_OK;
@@ -840,7 +841,7 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         // ring depth: four stages when four CTAs of them still fit an SM's shared memory, else three (swept on the
         // 64-layer stack: deeper rings with fewer resident CTAs were slower overall)
         const int stage_bytes = p.wbytes_max + 8 * mt * GQ_XROW_BYTES;
-        p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? 4096 : 0) + GQ_CONSUMER_WARPS * mt * 512) <= 227 * 1024) ? 4 : 3;
+        p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) + GQ_CONSUMER_WARPS * mt * 512) <= 227 * 1024) ? 4 : 3;
         static int forced = -1;   // tuning knob: GQ_STAGES=n overrides the ring depth
         if (forced < 0) { const char *e = getenv("GQ_STAGES"); forced = e ? atoi(e) : 0; }
         if (forced >= 2 && forced <= 8) p.stages = forced;
@@ -848,10 +849,10 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     int rc = GQ_OK;
     if (phases & 2) {
         switch (mt) {
-            case 1: rc = launch_gemv<1>(p, n_desc, st); break;
-            case 2: rc = launch_gemv<2>(p, n_desc, st); break;
-            case 4: rc = launch_gemv<4>(p, n_desc, st); break;
-            default: rc = launch_gemv<8>(p, n_desc, st); break;
+            case 1: rc = launch_gemv<1, 4>(p, n_desc, st); break;
+            case 2: rc = launch_gemv<2, 0>(p, n_desc, st); break;
+            case 4: rc = launch_gemv<4, 0>(p, n_desc, st); break;
+            default: rc = launch_gemv<8, 0>(p, n_desc, st); break;
         }
     }
     if (rc) return rc;
@@ -1035,7 +1036,7 @@ extern "C" int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K) {
 template <int NB>
 static int launch_prefill(const PrefillParams &p, const __nv_bfloat16 *x, int64_t ldx, float *ex, uint8_t *xp, cudaStream_t st) {
     const int mt = (p.M + NB - 1) / NB;
-    const size_t smem = 1024 + (size_t)GQ_PF_STAGES * (GQ_PF_A_BYTES + NB * 128) + 128 + 4096;
+    const size_t smem = 1024 + (size_t)GQ_PF_STAGES * (GQ_PF_A_BYTES + NB * 128) + 128 + GQ_IQ3S_SMEM_BYTES;
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));

@@ -18,7 +18,7 @@
 // device status word values (positive)
 #define GQ_DEV_TIMEOUT 1
 
-#define GQ_SPIN_LIMIT (1u << 24)   // iterations of a try_wait loop before a kernel gives up and reports GQ_DEV_TIMEOUT
+#define GQ_SPIN_LIMIT (1u << 30)   // polls of a try_wait loop before a kernel gives up and reports GQ_DEV_TIMEOUT (the time limit ends it first)
 
 namespace gq {
 
@@ -46,11 +46,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within GQ_SPIN_LIMIT polls (the caller records the
-// failure in the launch's status word and leaves; no wait in this library spins without a limit).
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false if the phase did not complete within GQ_WAIT_LIMIT_NS (or GQ_SPIN_LIMIT polls, whichever ends
+// first); the caller records the failure in the launch's status word and leaves.  No wait in this library spins
+// without a limit.  The limit is wall time, and generous, because under programmatic dependent launch a consumer
+// may already be waiting while the kernel in front of this one still runs.
+#define GQ_WAIT_LIMIT_NS 4000000000ull
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < GQ_SPIN_LIMIT; ++i)
+    for (uint32_t i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t i = 0; i < GQ_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && global_timer_ns() - t0 > GQ_WAIT_LIMIT_NS) return false;
+    }
     return false;
 }
 

@@ -636,6 +636,7 @@ struct Dec<GQ_Q3_K> {
     template <int R> static constexpr float offs() { return float((1024 >> (2 * ((R >> 1) & 3))) + 4); }
 };
 
+#define GQ_IQ3S_SMEM_BYTES 4096
 // ---- IQ3_S ----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_IQ3_S> {
@@ -696,5 +697,14 @@ struct Dec<GQ_IQ3_S> {
     static constexpr bool HAS_MIN = false;
     template <int R> static constexpr float offs() { return 0.0f; }
 };
+
+
+// one entry of the IQ3_S shared-memory grid: the four magnitude bytes of a grid word as two fp16 pairs
+GQ_HD inline uint2 iq3s_grid_entry(uint32_t w) {
+    uint2 e;
+    e.x = h2_as_u32(__floats2half2_rn((float)(w & 0xFF), (float)((w >> 8) & 0xFF)));
+    e.y = h2_as_u32(__floats2half2_rn((float)((w >> 16) & 0xFF), (float)(w >> 24)));
+    return e;
+}
 
 }  // namespace gq

@@ -169,13 +169,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, 1) gemm_prefill_kernel(const Pr
         fence_barrier_init();
     }
     if (d0[1] == GQ_IQ3_S || d1[1] == GQ_IQ3_S) {
-        for (int i = threadIdx.x; i < 512; i += blockDim.x) {
-            const uint32_t w = c_iq3s_grid[i];
-            uint2 e;
-            e.x = h2_as_u32(__floats2half2_rn((float)(w & 0xFF), (float)((w >> 8) & 0xFF)));
-            e.y = h2_as_u32(__floats2half2_rn((float)((w >> 16) & 0xFF), (float)(w >> 24)));
-            grid_s[i] = e;
-        }
+        for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]);
     }
     if (!has1) {
         // rows 64..127 of every A stage are never written: clear them once

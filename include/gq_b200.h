@@ -80,7 +80,8 @@ int64_t gq_desc_rows(int n_shards, const int64_t *n_outs, int split);
 int64_t gq_build_descs(int n_shards, const int32_t *types, const int64_t *n_outs, int64_t K, int split, int32_t *desc_host);
 
 /* Split-K of a grouped launch: n_tiles output tiles, nb k-blocks, M batch rows, avg_bytes_per_256 of
- * the run, on a device with sm_count SMs.  Always in [1, nb].
+ * the run, on a device with sm_count SMs.  Always in [1, nb] and at most 8 (the split then stays inside
+ * one thread-block cluster); any other value in [1, nb] is also valid for the calls below.
  * Reference: grouped_split_for (gguf-plugin/gluon/tiles_grouped.py:209-250), re-derived for 148 SMs. */
 int gq_split_for(int64_t n_tiles, int64_t nb, int64_t M, int avg_bytes_per_256, int sm_count);
 
@@ -100,8 +101,9 @@ int64_t gq_workspace_bytes(int64_t M, int64_t K, int64_t n_total, int split);
  *   run_info  gq_run_info of the run's types
  *   y_dev     bf16, row stride ldy elements; the run writes columns [0, n_total)
  *   workspace_dev  at least gq_workspace_bytes(M, K, n_total, split) bytes, 256-byte aligned
- * Launches: activation preparation, the grouped kernel, and (split > 1) the partial sum.  M == 0 is a
- * no-op.  Reference: gluon_mul_mat_tiles_grouped for M <= 32 and the bm-64 wide form
+ * Launches: activation preparation and the grouped kernel; splits up to 8 are reduced inside the kernel
+ * (one thread-block cluster per tile, fixed summation order), larger ones by a third launch that sums fp32
+ * partials from the workspace.  M == 0 is a no-op.  Reference: gluon_mul_mat_tiles_grouped for M <= 32 and the bm-64 wide form
  * (gguf-plugin/gluon/interface.py:141-188), quantize_activations_256, grouped_gemm, sum_partials
  * (gguf-plugin/gluon/tiles_grouped.py:110-162,1204-1275). */
 int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
