@@ -124,6 +124,9 @@ def cpu_sample(m: int, n_layers: int, target_s: float = 0.0):
     return passes * nbytes / dt / 1e9, dt / passes, info
 
 
+_emit = print      # replaced in main() by a writer to the process's original stdout
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -143,7 +146,7 @@ def run_reference(args):
                        "sample": "each step a bounded sample of that workload on the host cores: 1 of its 64 blocks, passed over for about 10 s"},
             "cpu_baseline": dict(info, value=value, unit="GB/s"),
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    _emit(json.dumps(line))
 
 
 def run_ours(args):
@@ -173,7 +176,7 @@ def run_ours(args):
     L = _lib.lib()
     st = S.LinearStack(n_layers=args.layers, device=dev, tp_rank=rank, tp_size=world)
     m = args.m
-    st.enable_prefetch(not args.no_l2_prefetch)
+    st.enable_prefetch(args.l2_prefetch and not args.no_l2_prefetch)
     x_dev = st.make_inputs(m)
     x_host = {k: v.cpu().pin_memory() for k, v in x_dev.items()}
     out_host = torch.empty((m, st.hidden), dtype=torch.bfloat16).pin_memory()
@@ -334,7 +337,7 @@ def run_ours(args):
         if world == 1 and not args.no_cpu:
             v, dt, info = cpu_sample(m, 2, target_s=12.0)
             line["cpu_baseline"] = dict(info, value=v, unit="GB/s")
-        print(json.dumps(line), flush=True)
+        _emit(json.dumps(line))
     if world > 1:
         # leave without tearing NCCL down: destroying a process group whose collectives live inside captured
         # CUDA graphs can block forever, and nothing is left to do
@@ -356,8 +359,16 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill TFLOP/s leg")
     ap.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: use NCCL for the row-parallel all-reduce instead of the library's push kernel")
-    ap.add_argument("--no-l2-prefetch", action="store_true", help="do not warm the L2 with the next layer's weights")
+    ap.add_argument("--l2-prefetch", action="store_true", help="warm the L2 with the next layer's weights from the idle producer lanes (measured neutral)")
+    ap.add_argument("--no-l2-prefetch", action="store_true", help="accepted for older command lines; the prefetch is off unless --l2-prefetch is given")
     args = ap.parse_args()
+    # stdout carries the one JSON line and nothing else: whatever libraries print there (NCCL's version banner, for
+    # one) goes to stderr instead, for the whole run and at the file-descriptor level
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    global _emit
+    _emit = lambda text: os.write(json_fd, (text + "\n").encode())
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -19,6 +19,7 @@ from ._lib import DESC_WORDS, MAX_GEMV_ROWS, GqError, check, lib
 
 TILE_TYPES = F.SUPPORTED_TYPES   # every one of the eleven types is held tile-major (the reference: GLUON_TILE_TYPES)
 GEMV_MAX_ROWS = MAX_GEMV_ROWS    # row-count dispatch threshold: above it the prefill kernel takes over
+WIDE_MIN_ROWS = 32               # ... and above this one already, when the run has at least two tiles per SM
 
 
 def _stream_ptr(t: torch.Tensor) -> int:
@@ -242,15 +243,20 @@ def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[tor
                           tiles: list[torch.Tensor], n_outs: list[int], weight_types: list[int], nb: int, block_bytes: int) -> torch.Tensor:
     """A layer's run of shards in one call: x bf16 [M, K] -> [M, sum(n_outs)] (reference:
     gluon_mul_mat_tiles_grouped, gguf-plugin/gluon/interface.py:141-188).  The row-count dispatch lives
-    here, inside the op: up to 64 rows one grouped launch at the split of the table for that row count;
-    above, the tcgen05 dequant-GEMM (weights dequantised into shared memory once per 256 batch rows)."""
+    here, inside the op: up to 64 rows one grouped launch at the split of the table for that row count
+    (up to 32 rows for runs of at least two tiles per SM); above, the tcgen05 dequant-GEMM (weights
+    dequantised into shared memory once per 256 batch rows)."""
     m = int(x.shape[0])
     n_total = sum(int(n) for n in n_outs)
     out = torch.empty((m, n_total), dtype=x.dtype, device=x.device)
     if m == 0:
         return out
     n_tiles = sum(-(-int(n) // 64) for n in n_outs)
-    if m <= GEMV_MAX_ROWS:
+    # 33..64 rows: the grouped kernel re-reads a 39 KB activation tile per k-block and CTA there and is bound by
+    # that; a run wide enough to give every SM a CTA of the tcgen05 kernel (two tiles each) is faster on it
+    # (gate_up at 48-64 rows: 110 vs 140 us)
+    wide = m > WIDE_MIN_ROWS and n_tiles >= 2 * sm_count(x.device)
+    if m <= GEMV_MAX_ROWS and not wide:
         s = grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=sm_count(x.device))
         if s not in desc_splits:
             s = 1

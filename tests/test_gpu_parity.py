@@ -317,6 +317,22 @@ def test_prefill_mixed_run_and_dispatch_boundary():
                 col += n
 
 
+def test_wide_run_dispatch_takes_the_tcgen05_path_from_33_rows():
+    """A run of at least two tiles per SM goes to the tcgen05 kernel already at 33..64 rows: same tolerance, and
+    bit-identical to calling that kernel directly; at 32 rows it is still the grouped kernel."""
+    n_out, k, t = 64 * 2 * ops.sm_count(dev()), 512, F.Q4_K
+    raw = synth.random_blocks(n_out, k, t, seed=77)
+    tl = ops.repack_tiles(raw.to(dev()), n_out, t)
+    packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer([tl], [n_out], [t])
+    d1 = descs[splits.index(1)]
+    for m in (32, 33, 64):
+        x = synth.activations(m, k, device=dev())
+        y = ops.fused_mul_mat_gguf_tiles_grouped(x, packed, descs, splits, views, [n_out], [t], nb, bb)
+        assert oracle.rel_err(y.float().cpu().numpy(), ref_gemm(x, raw, t)) < TOL_TIGHT
+        same = torch.equal(y, ops.prefill_gemm(x, packed, d1, n_out))
+        assert same == (m > 32)
+
+
 def test_prefill_full_size_down_projection_properties():
     """BASELINE configs[2] shape (down: K 17408, N 5120, Q6_K) at M = 2048: a row/column subset against the
     oracle and linearity in x at full size."""
