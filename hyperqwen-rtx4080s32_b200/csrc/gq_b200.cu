@@ -841,7 +841,8 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         // ring depth: four stages when four CTAs of them still fit an SM's shared memory, else three (swept on the
         // 64-layer stack: deeper rings with fewer resident CTAs were slower overall)
         const int stage_bytes = p.wbytes_max + 8 * mt * GQ_XROW_BYTES;
-        p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) + GQ_CONSUMER_WARPS * mt * 512) <= 227 * 1024) ? 4 : 3;
+        // (an SM has 228 KB of shared memory and the system keeps 1 KB of it per resident CTA)
+        p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) + GQ_CONSUMER_WARPS * mt * 512 + 1024) <= 228 * 1024) ? 4 : 3;
         static int forced = -1;   // tuning knob: GQ_STAGES=n overrides the ring depth
         if (forced < 0) { const char *e = getenv("GQ_STAGES"); forced = e ? atoi(e) : 0; }
         if (forced >= 2 && forced <= 8) p.stages = forced;
