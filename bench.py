@@ -175,6 +175,9 @@ def run_ours(args):
             _tp.enable_push_all_reduce(max_bytes=max(64, args.m) * 5120 * 2)
     L = _lib.lib()
     st = S.LinearStack(n_layers=args.layers, device=dev, tp_rank=rank, tp_size=world)
+    fused = world > 1 and not args.nccl_allreduce and not args.unfused_allreduce and args.m <= 64
+    if fused:
+        st.enable_fused_all_reduce(max_m=64)
     m = args.m
     st.enable_prefetch(args.l2_prefetch and not args.no_l2_prefetch)
     x_dev = st.make_inputs(m)
@@ -317,7 +320,7 @@ def run_ours(args):
                 "data": "synthetic",
                 "config": {"workload": f"mixed-type {args.layers}-layer GGUF decoder linear stack (BASELINE configs[3]{'/[4] tensor-parallel' if world > 1 else ''}), decode M={m}",
                            "bits_per_weight": round(8 * total_bytes / st.weights_full, 3), "raw_block_bytes": total_bytes,
-                           "l2": "weights (10 GB) far exceed L2; no flush needed", "parallelism": f"tp{world}", "all_reduce": ("none" if world == 1 else "nccl" if args.nccl_allreduce else "push kernel over NVLink peer memory (gq_allreduce_push)"),
+                           "l2": "weights (10 GB) far exceed L2; no flush needed", "parallelism": f"tp{world}", "all_reduce": ("none" if world == 1 else "nccl" if args.nccl_allreduce else "fused into the grouped kernel's epilogue, pushed over NVLink peer memory (gq_gemv_grouped_allreduce)" if fused else "push kernel over NVLink peer memory (gq_allreduce_push)"),
                            "cuda_graph": bool(captured), "l2_prefetch_next_layer": bool(st.prefetch),
                            "weights": "random valid blocks (the reference's test method), seeded"},
                 "tokens_per_s": m / (ms_step * 1e-3),
@@ -358,6 +361,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill TFLOP/s leg")
+    ap.add_argument("--unfused-allreduce", action="store_true", help="tensor parallel: all-reduce with the library's separate push kernel instead of inside the grouped kernel")
     ap.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: use NCCL for the row-parallel all-reduce instead of the library's push kernel")
     ap.add_argument("--l2-prefetch", action="store_true", help="warm the L2 with the next layer's weights from the idle producer lanes (measured neutral)")
     ap.add_argument("--no-l2-prefetch", action="store_true", help="accepted for older command lines; the prefetch is off unless --l2-prefetch is given")

@@ -341,6 +341,19 @@ __global__ void __launch_bounds__(GQ_PREP_THREADS) prep_x_kernel(const __nv_bflo
 // Replaces tiles_grouped_kernel / _run (gguf-plugin/gluon/tiles_grouped.py:343-1201).
 // ---------------------------------------------------------------------------------------------------
 #define GQ_CONSUMER_WARPS 4
+#define GQ_AR_MAX_WORLD 8
+
+// Peer buffers of the fused multiply + all-reduce (row-parallel layers under tensor parallelism).  A rank's buffer:
+// [per-unit call counters u32][flags: 2 sets x world x units u32] padded to 4096, then data: 2 sets x world slots of
+// slot_bytes, a slot being a bf16 [M][n_total] image of one rank's partial output.  A unit is (output tile, consumer
+// warp): 16 output columns of all batch rows — the grain at which ranks exchange and sum.
+struct ArFused {
+    int world, rank, units;          // world == 0: plain output, no exchange
+    int64_t slot_bytes;
+    uint8_t *buf[GQ_AR_MAX_WORLD];
+    uint32_t *flags[GQ_AR_MAX_WORLD];
+    uint32_t *counters;
+};
 
 struct GemvParams {
     const uint8_t *packed;
@@ -357,6 +370,7 @@ struct GemvParams {
     int cluster;         // 1: the `split` CTAs of a tile form a thread-block cluster and reduce through shared memory
     const uint8_t *pf_ptr;   // weights the caller will multiply next (or null): prefetched into L2 while this launch computes
     int64_t pf_bytes;
+    ArFused ar;
 };
 
 template <int TYPE, int MT, int P>
@@ -462,13 +476,101 @@ __device__ __forceinline__ bool consume(const uint8_t *smem, uint64_t *full, uin
     return true;
 }
 
+// One warp's share of the fused all-reduce.  `blk` (shared memory) holds the warp's bf16 block [M][16] of this
+// rank's partial output (columns col .. col + ncols - 1 of every batch row).  Push based, one shot: the block goes
+// into this rank's slot of every rank's buffer (plain stores through peer pointers, own buffer included), a flag
+// per (rank, unit) follows with release semantics at system scope, the warp waits — with a time limit — for the same
+// unit of every other rank, then sums the slots from its OWN memory in rank order (fp32, one bf16 rounding) into y.
+// No loads from remote memory, no multicast.  The call number lives in device memory per unit and selects one of
+// two slot sets, so a captured CUDA graph replays correctly; a rank cannot run two calls ahead of a peer because
+// each call needs every peer's flags of that call.
+__device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const __nv_bfloat16 *blk, int unit, int col, int ncols, int lane) {
+    const ArFused &a = p.ar;
+    uint32_t seq = 0;
+    if (lane == 0) seq = a.counters[unit] + 1;
+    seq = __shfl_sync(0xffffffffu, seq, 0);
+    const uint32_t set = seq & 1u;
+    const int M = p.M;
+    const int64_t nt = p.n_total;
+    const bool vec = ncols == 16 && !(col & 7) && !(nt & 7);     // 16-byte pieces: 8 columns of one batch row
+    for (int pr = 0; pr < a.world; ++pr) {
+        uint8_t *dst = a.buf[pr] + ((int64_t)set * a.world + a.rank) * a.slot_bytes;
+        if (vec) {
+            for (int piece = lane; piece < 2 * M; piece += 32) {
+                const int n = piece >> 1, h = piece & 1;
+                *reinterpret_cast<uint4 *>(dst + ((int64_t)n * nt + col + 8 * h) * 2) = *reinterpret_cast<const uint4 *>(blk + n * 16 + 8 * h);
+            }
+        } else {
+            for (int e = lane; e < 16 * M; e += 32) {
+                const int n = e >> 4, c = e & 15;
+                if (c < ncols) reinterpret_cast<__nv_bfloat16 *>(dst)[(int64_t)n * nt + col + c] = blk[n * 16 + c];
+            }
+        }
+    }
+    __threadfence_system();
+    __syncwarp();
+    bool fail = false;
+    if (lane < a.world) {
+        uint32_t *f = a.flags[lane] + ((int64_t)set * a.world + a.rank) * a.units + unit;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+        const uint32_t *mine = a.flags[a.rank] + ((int64_t)set * a.world + lane) * a.units + unit;
+        const uint64_t t0 = global_timer_ns();
+        uint32_t v, it = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v == seq) break;
+            if ((++it & 63u) == 0 && global_timer_ns() - t0 > GQ_WAIT_LIMIT_NS) { fail = true; break; }
+        }
+    }
+    fail = __any_sync(0xffffffffu, fail);
+    if (fail) {
+        if (lane == 0) { atomicExch(p.status, GQ_DEV_TIMEOUT); a.counters[unit] = seq; }
+        return;
+    }
+    const uint8_t *base = a.buf[a.rank] + (int64_t)set * a.world * a.slot_bytes;
+    if (vec) {
+        for (int piece = lane; piece < 2 * M; piece += 32) {
+            const int n = piece >> 1, h = piece & 1;
+            const int64_t off = ((int64_t)n * nt + col + 8 * h) * 2;
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < a.world; ++r) {
+                const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(base + (int64_t)r * a.slot_bytes + off));
+                const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); sum[2 * j] += f.x; sum[2 * j + 1] += f.y; }
+            }
+            __nv_bfloat16 *yp = p.y + (int64_t)n * p.ldy + col + 8 * h;
+            if (!(reinterpret_cast<uintptr_t>(yp) & 15)) {
+                uint4 o;
+                __nv_bfloat162 *ob = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(sum[2 * j], sum[2 * j + 1]);
+                *reinterpret_cast<uint4 *>(yp) = o;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) yp[j] = __float2bfloat16_rn(sum[j]);
+            }
+        }
+    } else {
+        for (int e = lane; e < 16 * M; e += 32) {
+            const int n = e >> 4, c = e & 15;
+            if (c >= ncols) continue;
+            float sum = 0.f;
+            for (int r = 0; r < a.world; ++r)
+                sum += __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16 *>(base + (int64_t)r * a.slot_bytes) + (int64_t)n * nt + col + c));
+            p.y[(int64_t)n * p.ldy + col + c] = __float2bfloat16_rn(sum);
+        }
+    }
+    if (lane == 0) a.counters[unit] = seq;
+}
+
 // MINB = CTAs per SM the compiler must leave room for (0: its own choice).  For the M <= 8 form 4 gives it 96
 // registers, which it turns into more loads and MMAs in flight per warp: measured 14 % faster than the 72-register
 // build when a CTA walks ten or more k-blocks, a little slower on launches of many short CTAs, 2 % faster on the
 // mixed stack.  (Compiling both and choosing per call was slower than either alone: alternating between two large
 // kernels costs more in instruction-cache misses at every launch than the better fit gains.)
 template <int MT, int MINB>
-__global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_grouped_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_grouped_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: [stages x (weights wbytes_max | activation tile)] [full barriers] [empty barriers] [IQ3_S grid]
     const int stages = p.stages, wmax = p.wbytes_max, M = p.M;
@@ -567,11 +669,12 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
 
     // ---- epilogue: rows of the MMA are output columns, columns of the MMA are batch rows ----
     const int g = lane >> 2, t = lane & 3;
+    // scratch of its own behind the ring (a slower warp may still read the ring): GQ_CONSUMER_WARPS x MT x 512 bytes
+    float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0));
     if (p.cluster) {
         // split-K inside a cluster: every CTA parks its accumulators in its own shared memory (the stage ring is
         // idle by now), the CTA of split 0 adds the others' in split order through distributed shared memory and
         // writes bf16 once.  No partial sums in HBM, no second kernel; the order of the additions is fixed.
-        float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0));   // its own area: a slower warp may still read the ring
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt) red[(warp * MT + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
         cluster_sync_all();
@@ -588,6 +691,23 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         }
         cluster_sync_all();      // peers stay resident until their shared memory has been read
         if (split_idx != 0) return;
+    }
+    if (p.ar.world > 0 && (p.split == 1 || p.cluster)) {
+        // tensor parallel, row-parallel layer: this rank's partial output does not go to y but, as bf16, through
+        // the warp's scratch to every rank; y receives the sum over ranks (fused_allreduce_block)
+        __nv_bfloat16 *blk = reinterpret_cast<__nv_bfloat16 *>(reinterpret_cast<uint8_t *>(red) + warp * MT * 512);
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int rl = g + 8 * (j >> 1), n = nt * 8 + 2 * t + (j & 1);
+                const bool valid = ok && warp * 16 + rl < nvalid && n < p.M;
+                blk[n * 16 + rl] = __float2bfloat16_rn(valid ? acc[nt][j] * p.ex[n] : 0.0f);
+            }
+        __syncwarp();
+        const int ncols = nvalid - warp * 16 < 16 ? nvalid - warp * 16 : 16;
+        if (ncols > 0) fused_allreduce_block(p, blk, (int)(blockIdx.x / (unsigned)p.split) * GQ_CONSUMER_WARPS + warp, col0 + warp * 16, ncols, lane);
+        return;
     }
 #pragma unroll
     for (int nt = 0; nt < MT; ++nt)
@@ -799,7 +919,8 @@ extern "C" int gq_run_info(int n_shards, const int32_t *types) {
 
 static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
                              int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
-                             int64_t workspace_bytes, void *stream, int phases, const void *next_packed_dev, int64_t next_bytes) {
+                             int64_t workspace_bytes, void *stream, int phases, const void *next_packed_dev, int64_t next_bytes,
+                             const ArFused *ar = nullptr) {
     if (M < 0 || M > GQ_MAX_GEMV_ROWS || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0 || split < 1) return GQ_ERR_SHAPE;
     if (M == 0 || n_total == 0 || n_desc == 0) return GQ_OK;
     if (!x_dev || !packed_dev || !desc_dev || !y_dev || !workspace_dev) return GQ_ERR_ARG;
@@ -836,6 +957,13 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     p.cluster = (split > 1 && split <= 8 && n_desc % split == 0) ? 1 : 0;
     p.pf_ptr = (next_packed_dev && next_bytes > 0 && !((uintptr_t)next_packed_dev & 15)) ? (const uint8_t *)next_packed_dev : nullptr;
     p.pf_bytes = next_bytes;
+    if (ar) {
+        if (split > 1 && !p.cluster) return GQ_ERR_ARG;        // the exchange needs the whole tile sum in one CTA
+        if (n_desc / split * GQ_CONSUMER_WARPS > ar->units) return GQ_ERR_LIMIT;
+        p.ar = *ar;
+    } else {
+        p.ar = ArFused{};
+    }
     const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
     {
         // ring depth: four stages when four CTAs of them still fit an SM's shared memory, else three (swept on the
@@ -920,6 +1048,41 @@ extern "C" int gq_gemv_grouped_static(const void *x_dev, int64_t M, int64_t K, i
                                   GQ_STATIC_WS_BYTES, stream, 7);
 }
 
+// ---- the same call fused with the all-reduce of a row-parallel layer ---------------------------------------
+// Every rank multiplies its K shard; the kernel's epilogue exchanges the bf16 partial outputs through peer memory
+// and leaves the sum over ranks in y on every rank (fused_allreduce_block).  Same arithmetic as the grouped call
+// followed by gq_allreduce_push, without the second launch and its latency.
+static int64_t fused_ar_units(int64_t max_n_total) { return (max_n_total / 64 + 16) * GQ_CONSUMER_WARPS; }
+static int64_t fused_ar_header(int world, int64_t max_n_total) {
+    return (4 * fused_ar_units(max_n_total) * (1 + 2 * (int64_t)world) + 4095) & ~(int64_t)4095;
+}
+
+extern "C" int64_t gq_fused_allreduce_buffer_bytes(int world, int64_t max_m, int64_t max_n_total) {
+    if (world < 1 || world > GQ_AR_MAX_WORLD || max_m < 1 || max_m > GQ_MAX_GEMV_ROWS || max_n_total < 1) return GQ_ERR_ARG;
+    return fused_ar_header(world, max_n_total) + 2 * (int64_t)world * align256(max_m * max_n_total * 2);
+}
+
+extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                                         int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                                         void *workspace_dev, int64_t workspace_bytes, int rank, int world, const uint64_t *peer_buffers,
+                                         int64_t max_m, int64_t max_n_total, void *stream) {
+    if (world < 1 || world > GQ_AR_MAX_WORLD || rank < 0 || rank >= world || !peer_buffers) return GQ_ERR_ARG;
+    if (max_m < 1 || max_m > GQ_MAX_GEMV_ROWS || M > max_m || n_total > max_n_total) return GQ_ERR_SHAPE;
+    ArFused ar = {};
+    ar.world = world; ar.rank = rank; ar.units = (int)fused_ar_units(max_n_total);
+    ar.slot_bytes = align256(max_m * max_n_total * 2);
+    const int64_t header = fused_ar_header(world, max_n_total);
+    for (int p = 0; p < world; ++p) {
+        if (!peer_buffers[p] || (peer_buffers[p] & 255)) return GQ_ERR_ARG;
+        uint8_t *b = reinterpret_cast<uint8_t *>(peer_buffers[p]);
+        ar.flags[p] = reinterpret_cast<uint32_t *>(b) + ar.units;
+        ar.buf[p] = b + header;
+    }
+    ar.counters = reinterpret_cast<uint32_t *>(peer_buffers[rank]);
+    return gemv_grouped_impl(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
+                             workspace_bytes, stream, 7, nullptr, 0, &ar);
+}
+
 // ---- small-message all-reduce over peer memory (tensor-parallel row-parallel layers) ---------------------
 // One-shot, push based: every rank stores its bf16 vector into its slot of every peer's buffer (plain stores
 // over NVLink into memory the peers mapped for each other), publishes a per-CTA flag, waits — with a limit —
@@ -927,7 +1090,6 @@ extern "C" int gq_gemv_grouped_static(const void *x_dev, int64_t M, int64_t K, i
 // rounding).  No loads from remote memory, no multicast.  Two slot sets alternate by call parity; the call
 // number lives in device memory (one counter per CTA) so a captured CUDA graph replays correctly.
 // The reference has no collective of its own on this path (docs/multi-gpu.md:8-13 leaves it to vLLM's NCCL).
-#define GQ_AR_MAX_WORLD 8
 #define GQ_AR_CTAS 16
 #define GQ_AR_SPIN_LIMIT (1u << 25)
 

@@ -8,6 +8,8 @@ memory.  There is no fallback: a missing library or a CPU tensor raises.
 """
 from __future__ import annotations
 
+import contextlib
+
 import ctypes
 from typing import Sequence
 
@@ -178,11 +180,29 @@ def clear_prefetch_chain() -> None:
     _NEXT_WEIGHTS.clear()
 
 
+_FUSED_AR = None      # the tp.FusedAllReduce in force for the calls inside `with fused_allreduce(ctx)`
+
+
+@contextlib.contextmanager
+def fused_allreduce(ctx):
+    """Inside this block the small-batch path of mul_mat_tiles_grouped leaves the SUM over the tensor-parallel
+    ranks in its output (gq_gemv_grouped_allreduce) and sets ctx.used; calls it cannot serve (more than 64 rows,
+    sizes beyond the context's buffers) run as usual and leave ctx.used alone, so the caller can fall back to a
+    separate all-reduce."""
+    global _FUSED_AR
+    prev, _FUSED_AR = _FUSED_AR, ctx
+    try:
+        yield ctx
+    finally:
+        _FUSED_AR = prev
+
+
 def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, split: int, wtypes: Sequence[int], n_total: int,
-                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, phases: int = 7) -> torch.Tensor:
+                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, phases: int = 7, allreduce=None) -> torch.Tensor:
     """One grouped launch for 1..64 rows: x bf16 [M, K] -> out bf16 [M, n_total] (out may be a column view).
     `workspace` (uint8, 256-byte aligned, at least gq_workspace_bytes) is allocated per call unless given;
-    `phases` selects the launches (1 prepare activations, 2 grouped kernel, 4 partial sum)."""
+    `phases` selects the launches (1 prepare activations, 2 grouped kernel, 4 partial sum); `allreduce` (a
+    tp.FusedAllReduce) makes the output the sum over the tensor-parallel ranks."""
     _need_cuda(x, "x")
     if x.dtype != torch.bfloat16 or x.dim() != 2:
         raise GqError(f"x must be bf16 [M, K], got {x.dtype} {tuple(x.shape)}")
@@ -200,6 +220,14 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
     L = lib()
     ws_bytes = check(L.gq_workspace_bytes(m, k, n_total, int(split)), "gq_workspace_bytes")
     ws = workspace if workspace is not None else torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    if allreduce is not None:
+        with torch.cuda.device(x.device):
+            check(L.gq_gemv_grouped_allreduce(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc.data_ptr(), int(desc.shape[0]), int(split),
+                                              run_info(wtypes), out.data_ptr(), out.stride(0), n_total, ws.data_ptr(), ws.numel(),
+                                              allreduce.rank, allreduce.world, allreduce.ptrs, allreduce.max_m, allreduce.max_n_total,
+                                              _stream_ptr(x)), "gq_gemv_grouped_allreduce")
+        allreduce.used = True
+        return out
     nxt = _NEXT_WEIGHTS.get(packed.data_ptr()) if phases == 7 else None
     if nxt is not None:
         with torch.cuda.device(x.device):
@@ -260,7 +288,10 @@ def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[tor
         s = grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=sm_count(x.device))
         if s not in desc_splits:
             s = 1
-        grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, out=out)
+        ar = _FUSED_AR
+        if ar is not None and not (m <= ar.max_m and n_total <= ar.max_n_total and s <= 8):
+            ar = None
+        grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, out=out, allreduce=ar)
         return out
     prefill_gemm(x, packed, descs[desc_splits.index(1)], n_total, out=out)
     return out

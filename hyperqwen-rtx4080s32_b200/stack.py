@@ -91,16 +91,35 @@ class LinearStack:
 
     def step(self, x: dict[str, torch.Tensor]) -> torch.Tensor:
         """One pass: every linear of every block applied to the input of its name; returns the last
-        block's `down` output (under tensor parallelism: this rank's partial sum)."""
+        block's `down` output (under tensor parallelism: summed over the ranks)."""
         from . import tp as _tp
 
+        from . import ops
+
         out = None
+        far = getattr(self, "fused_ar", None)
         for blk in self.layers:
             for name in ("qkv", "o", "gate_up", "down"):
-                out = blk[name](x[name])
                 if self.tp_size > 1 and name in ("o", "down"):
-                    _tp.all_reduce_(out)
+                    if far is not None:
+                        # the all-reduce happens in the grouped kernel's epilogue; a call it cannot serve falls back
+                        far.used = False
+                        with ops.fused_allreduce(far):
+                            out = blk[name](x[name])
+                        if not far.used:
+                            _tp.all_reduce_(out)
+                    else:
+                        out = blk[name](x[name])
+                        _tp.all_reduce_(out)
+                else:
+                    out = blk[name](x[name])
         return out
+
+    def enable_fused_all_reduce(self, max_m: int = 64) -> None:
+        """Row-parallel layers sum over the ranks inside the grouped kernel (call on every rank, outside capture)."""
+        from . import tp as _tp
+
+        self.fused_ar = _tp.FusedAllReduce(max_m=max_m, max_n_total=self.hidden) if self.tp_size > 1 else None
 
     def make_inputs(self, m: int, seed: int = 0, device=None) -> dict[str, torch.Tensor]:
         """Seeded bf16 N(0, 1) inputs of every linear's (local, padded) K; row-parallel inputs are zero

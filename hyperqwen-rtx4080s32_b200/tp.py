@@ -110,6 +110,52 @@ class PushAllReduce:
         return t
 
 
+class FusedAllReduce:
+    """Peer buffers for the fused multiply + all-reduce of the row-parallel layers (gq_gemv_grouped_allreduce): the
+    grouped kernel's epilogue exchanges the ranks' bf16 partial outputs and leaves their sum in the output, so a
+    decode step needs no all-reduce launch at all.  One instance serves every row-parallel layer of up to
+    `max_m` rows and `max_n_total` output columns; use it through `ops.fused_allreduce(ctx)`."""
+
+    def __init__(self, max_m: int = 64, max_n_total: int = 5120, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from ._lib import check, lib
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.max_m, self.max_n_total = int(max_m), int(max_n_total)
+        nbytes = check(lib().gq_fused_allreduce_buffer_bytes(self.world, self.max_m, self.max_n_total), "gq_fused_allreduce_buffer_bytes")
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.buf.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert len(ptrs) == self.world and ptrs[self.rank] == self.buf.data_ptr()
+        self.ptrs = (ctypes.c_uint64 * self.world)(*ptrs)
+        self.used = False
+
+
+class LocalFusedAllReduce:
+    """The same context for a single process (world size 1, ordinary device memory): the exchange degenerates to a
+    round trip through the rank's own buffer.  For tests on one GPU."""
+
+    def __init__(self, max_m: int = 64, max_n_total: int = 5120, device=None):
+        import ctypes
+
+        from ._lib import check, lib
+
+        self.rank, self.world = 0, 1
+        self.max_m, self.max_n_total = int(max_m), int(max_n_total)
+        nbytes = check(lib().gq_fused_allreduce_buffer_bytes(1, self.max_m, self.max_n_total), "gq_fused_allreduce_buffer_bytes")
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device or torch.device("cuda", torch.cuda.current_device()))
+        self.ptrs = (ctypes.c_uint64 * 1)(self.buf.data_ptr())
+        self.used = False
+
+
 _FAST = None
 
 

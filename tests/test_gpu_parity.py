@@ -350,6 +350,50 @@ def test_prefill_full_size_down_projection_properties():
     assert float((y2 - 2 * y).abs().max()) <= 2 ** -7 * float(y.abs().max())
 
 
+def test_fused_all_reduce_single_rank_degenerate():
+    """gq_gemv_grouped_allreduce with one rank: the exchange is a round trip through the rank's own buffer, so the
+    output is bit-identical to the plain grouped call — for a cluster split, no split, a ragged last tile (scalar
+    path), a column-view output, several calls in a row (both slot sets) and a replayed CUDA graph."""
+    from hyperqwen_rtx4080s32_b200 import tp
+
+    ctx = tp.LocalFusedAllReduce(max_m=64, max_n_total=512, device=dev())
+    for (n_out, k, t) in [(256, 1024, F.Q4_K), (198, 768, F.IQ3_S), (512, 512, F.Q6_K)]:
+        raw = synth.random_blocks(n_out, k, t, seed=5)
+        tl = ops.repack_tiles(raw.to(dev()), n_out, t)
+        for s in (1, 2):
+            d = torch.from_numpy(ops.build_descs([t], [n_out], k, s)).to(dev())
+            for m in (1, 8, 17, 64):
+                x = synth.activations(m, k, device=dev())
+                want = ops.grouped_gemm(x, tl.reshape(-1), d, s, [t], n_out)
+                for rep in range(3):
+                    wide = torch.full((m, n_out + 24), float("nan"), dtype=torch.bfloat16, device=dev())
+                    got = ops.grouped_gemm(x, tl.reshape(-1), d, s, [t], n_out, out=wide[:, 8:8 + n_out], allreduce=ctx)
+                    assert torch.equal(got, want), f"{F.TYPE_NAMES[t]} n_out={n_out} split={s} M={m} rep={rep}"
+                    assert torch.isnan(wide[:, :8]).all() and torch.isnan(wide[:, 8 + n_out:]).all()
+    # through the op and a graph
+    n_out, k, t = 512, 1024, F.Q4_K
+    raw = synth.random_blocks(n_out, k, t, seed=6)
+    lin = GGUFLinear(k, [n_out])
+    lin.load_shard(raw.to(dev()), t)
+    lin.finalize()
+    x = synth.activations(8, k, device=dev())
+    want = lin(x)
+    with ops.fused_allreduce(ctx):
+        ctx.used = False
+        assert torch.equal(lin(x), want) and ctx.used
+        g = torch.cuda.CUDAGraph()
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(g, stream=stream):
+                y = lin(x)
+        torch.cuda.current_stream().wait_stream(stream)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y, want)
+
+
 def test_push_all_reduce_single_rank_degenerate(gq_lib):
     """The push all-reduce kernel with a world of one (its own buffer is the only peer): the result is the input,
     the per-CTA call counters advance, the slot sets alternate, and a replayed CUDA graph keeps working.  The
