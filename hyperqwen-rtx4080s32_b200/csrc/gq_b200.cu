@@ -344,14 +344,13 @@ __global__ void __launch_bounds__(GQ_PREP_THREADS) prep_x_kernel(const __nv_bflo
 #define GQ_AR_MAX_WORLD 8
 
 // Peer buffers of the fused multiply + all-reduce (row-parallel layers under tensor parallelism).  A rank's buffer:
-// [per-unit call counters u32][flags: 2 sets x world x units u32] padded to 4096, then data: 2 sets x world slots of
-// slot_bytes, a slot being a bf16 [M][n_total] image of one rank's partial output.  A unit is (output tile, consumer
-// warp): 16 output columns of all batch rows — the grain at which ranks exchange and sum.
+// [per-unit call counters u32] padded to 4096, then data: 2 sets x world slots of slot_bytes, a slot being an image
+// [M][n_total / 2] of 8-byte words {two bf16 values, call number} of one rank's partial output.  A unit is (output
+// tile, consumer warp): 16 output columns of all batch rows — the grain at which ranks exchange and sum.
 struct ArFused {
     int world, rank, units;          // world == 0: plain output, no exchange
     int64_t slot_bytes;
     uint8_t *buf[GQ_AR_MAX_WORLD];
-    uint32_t *flags[GQ_AR_MAX_WORLD];
     uint32_t *counters;
 };
 
@@ -477,91 +476,66 @@ __device__ __forceinline__ bool consume(const uint8_t *smem, uint64_t *full, uin
 }
 
 // One warp's share of the fused all-reduce.  `blk` (shared memory) holds the warp's bf16 block [M][16] of this
-// rank's partial output (columns col .. col + ncols - 1 of every batch row).  Push based, one shot: the block goes
-// into this rank's slot of every rank's buffer (plain stores through peer pointers, own buffer included), a flag
-// per (rank, unit) follows with release semantics at system scope, the warp waits — with a time limit — for the same
-// unit of every other rank, then sums the slots from its OWN memory in rank order (fp32, one bf16 rounding) into y.
-// No loads from remote memory, no multicast.  The call number lives in device memory per unit and selects one of
-// two slot sets, so a captured CUDA graph replays correctly; a rank cannot run two calls ahead of a peer because
-// each call needs every peer's flags of that call.
-__device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const __nv_bfloat16 *blk, int unit, int col, int ncols, int lane) {
+// rank's partial output (columns col .. col + ncols - 1 of every batch row; col and ncols even).  Push based, one
+// shot, and free of fences: every pair of bf16 values travels as one 8-byte word {values, call number}, stored
+// whole (an aligned 64-bit store is single-copy atomic) into this rank's slot of every rank's buffer — plain stores
+// through peer pointers, own buffer included.  The receiver polls the words of its OWN memory until their call
+// number is this call's (with a time limit), adds the ranks' values in rank order in fp32 and rounds once into y:
+// the data is its own flag, so no release / acquire at system scope is needed (on a busy SM those cost several
+// microseconds per warp).  No loads from remote memory, no multicast.  The call number lives in device memory per
+// (tile, warp) and selects one of two slot sets; a stale word of the same set carries an older number, and a rank
+// cannot run two calls ahead of a peer because each call needs every peer's words of that call.
+__device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const uint32_t *blk, int unit, int col, int ncols, int lane) {
     const ArFused &a = p.ar;
     uint32_t seq = 0;
     if (lane == 0) seq = a.counters[unit] + 1;
     seq = __shfl_sync(0xffffffffu, seq, 0);
     const uint32_t set = seq & 1u;
-    const int M = p.M;
-    const int64_t nt = p.n_total;
-    const bool vec = ncols == 16 && !(col & 7) && !(nt & 7);     // 16-byte pieces: 8 columns of one batch row
+    const int M = p.M, half = ncols >> 1;
+    const int64_t row_words = p.n_total >> 1, slot_words = a.slot_bytes >> 3;
+    const int64_t first = (int64_t)(col >> 1);
+    const int n_el = M * half;
     for (int pr = 0; pr < a.world; ++pr) {
-        uint8_t *dst = a.buf[pr] + ((int64_t)set * a.world + a.rank) * a.slot_bytes;
-        if (vec) {
-            for (int piece = lane; piece < 2 * M; piece += 32) {
-                const int n = piece >> 1, h = piece & 1;
-                *reinterpret_cast<uint4 *>(dst + ((int64_t)n * nt + col + 8 * h) * 2) = *reinterpret_cast<const uint4 *>(blk + n * 16 + 8 * h);
-            }
-        } else {
-            for (int e = lane; e < 16 * M; e += 32) {
-                const int n = e >> 4, c = e & 15;
-                if (c < ncols) reinterpret_cast<__nv_bfloat16 *>(dst)[(int64_t)n * nt + col + c] = blk[n * 16 + c];
-            }
+        unsigned long long *dst = reinterpret_cast<unsigned long long *>(a.buf[pr]) + ((int64_t)set * a.world + a.rank) * slot_words + first;
+        for (int e = lane; e < n_el; e += 32) {
+            const int n = e / half, c2 = e - n * half;
+            const unsigned long long w = (unsigned long long)blk[n * 8 + c2] | ((unsigned long long)seq << 32);
+            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst + n * row_words + c2), "l"(w) : "memory");
         }
     }
-    __threadfence_system();
-    __syncwarp();
+    const unsigned long long *src = reinterpret_cast<const unsigned long long *>(a.buf[a.rank]) + (int64_t)set * a.world * slot_words + first;
     bool fail = false;
-    if (lane < a.world) {
-        uint32_t *f = a.flags[lane] + ((int64_t)set * a.world + a.rank) * a.units + unit;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
-        const uint32_t *mine = a.flags[a.rank] + ((int64_t)set * a.world + lane) * a.units + unit;
-        const uint64_t t0 = global_timer_ns();
-        uint32_t v, it = 0;
-        for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-            if (v == seq) break;
-            if ((++it & 63u) == 0 && global_timer_ns() - t0 > GQ_WAIT_LIMIT_NS) { fail = true; break; }
+    uint64_t t0 = 0;
+    for (int e = lane; e < n_el; e += 32) {
+        const int n = e / half, c2 = e - n * half;
+        float s0 = 0.f, s1 = 0.f;
+        for (int r = 0; r < a.world; ++r) {
+            const unsigned long long *q = src + (int64_t)r * slot_words + n * row_words + c2;
+            unsigned long long w;
+            for (uint32_t it = 0;; ++it) {
+                asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(q) : "memory");
+                if ((uint32_t)(w >> 32) == seq) break;
+                if ((it & 255u) == 255u) {      // the clock is read only once a wait has become long
+                    const uint64_t now = global_timer_ns();
+                    if (t0 == 0) t0 = now;
+                    if (now - t0 > GQ_WAIT_LIMIT_NS) { fail = true; break; }
+                }
+            }
+            if (fail) break;
+            const uint32_t v = (uint32_t)w;
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v));
+            s0 += f.x; s1 += f.y;
         }
+        if (fail) break;
+        __nv_bfloat16 *yp = p.y + (int64_t)n * p.ldy + col + 2 * c2;
+        if (!(reinterpret_cast<uintptr_t>(yp) & 3)) *reinterpret_cast<__nv_bfloat162 *>(yp) = __floats2bfloat162_rn(s0, s1);
+        else { yp[0] = __float2bfloat16_rn(s0); yp[1] = __float2bfloat16_rn(s1); }
     }
     fail = __any_sync(0xffffffffu, fail);
-    if (fail) {
-        if (lane == 0) { atomicExch(p.status, GQ_DEV_TIMEOUT); a.counters[unit] = seq; }
-        return;
+    if (lane == 0) {
+        if (fail) atomicExch(p.status, GQ_DEV_TIMEOUT);
+        a.counters[unit] = seq;
     }
-    const uint8_t *base = a.buf[a.rank] + (int64_t)set * a.world * a.slot_bytes;
-    if (vec) {
-        for (int piece = lane; piece < 2 * M; piece += 32) {
-            const int n = piece >> 1, h = piece & 1;
-            const int64_t off = ((int64_t)n * nt + col + 8 * h) * 2;
-            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int r = 0; r < a.world; ++r) {
-                const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(base + (int64_t)r * a.slot_bytes + off));
-                const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&v);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); sum[2 * j] += f.x; sum[2 * j + 1] += f.y; }
-            }
-            __nv_bfloat16 *yp = p.y + (int64_t)n * p.ldy + col + 8 * h;
-            if (!(reinterpret_cast<uintptr_t>(yp) & 15)) {
-                uint4 o;
-                __nv_bfloat162 *ob = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(sum[2 * j], sum[2 * j + 1]);
-                *reinterpret_cast<uint4 *>(yp) = o;
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) yp[j] = __float2bfloat16_rn(sum[j]);
-            }
-        }
-    } else {
-        for (int e = lane; e < 16 * M; e += 32) {
-            const int n = e >> 4, c = e & 15;
-            if (c >= ncols) continue;
-            float sum = 0.f;
-            for (int r = 0; r < a.world; ++r)
-                sum += __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16 *>(base + (int64_t)r * a.slot_bytes) + (int64_t)n * nt + col + c));
-            p.y[(int64_t)n * p.ldy + col + c] = __float2bfloat16_rn(sum);
-        }
-    }
-    if (lane == 0) a.counters[unit] = seq;
 }
 
 // MINB = CTAs per SM the compiler must leave room for (0: its own choice).  For the M <= 8 form 4 gives it 96
@@ -694,7 +668,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     }
     if (p.ar.world > 0 && (p.split == 1 || p.cluster)) {
         // tensor parallel, row-parallel layer: this rank's partial output does not go to y but, as bf16, through
-        // the warp's scratch to every rank; y receives the sum over ranks (fused_allreduce_block)
+        // the warp's scratch to every rank; y receives the sum over ranks (fused_allreduce_tile)
         __nv_bfloat16 *blk = reinterpret_cast<__nv_bfloat16 *>(reinterpret_cast<uint8_t *>(red) + warp * MT * 512);
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt)
@@ -706,7 +680,11 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             }
         __syncwarp();
         const int ncols = nvalid - warp * 16 < 16 ? nvalid - warp * 16 : 16;
-        if (ncols > 0) fused_allreduce_block(p, blk, (int)(blockIdx.x / (unsigned)p.split) * GQ_CONSUMER_WARPS + warp, col0 + warp * 16, ncols, lane);
+        if (ncols > 0) {
+            if (((col0 | ncols | (int)p.n_total) & 1) && lane == 0) atomicExch(p.status, GQ_DEV_BAD_SHAPE);    // pairs of columns travel together
+            else fused_allreduce_block(p, reinterpret_cast<const uint32_t *>(blk), (int)(blockIdx.x / (unsigned)p.split) * GQ_CONSUMER_WARPS + warp,
+                                       col0 + warp * 16, ncols, lane);
+        }
         return;
     }
 #pragma unroll
@@ -1050,16 +1028,14 @@ extern "C" int gq_gemv_grouped_static(const void *x_dev, int64_t M, int64_t K, i
 
 // ---- the same call fused with the all-reduce of a row-parallel layer ---------------------------------------
 // Every rank multiplies its K shard; the kernel's epilogue exchanges the bf16 partial outputs through peer memory
-// and leaves the sum over ranks in y on every rank (fused_allreduce_block).  Same arithmetic as the grouped call
+// and leaves the sum over ranks in y on every rank (fused_allreduce_tile).  Same arithmetic as the grouped call
 // followed by gq_allreduce_push, without the second launch and its latency.
-static int64_t fused_ar_units(int64_t max_n_total) { return (max_n_total / 64 + 16) * GQ_CONSUMER_WARPS; }
-static int64_t fused_ar_header(int world, int64_t max_n_total) {
-    return (4 * fused_ar_units(max_n_total) * (1 + 2 * (int64_t)world) + 4095) & ~(int64_t)4095;
-}
+static int64_t fused_ar_units(int64_t max_n_total) { return (max_n_total / 64 + 64) * GQ_CONSUMER_WARPS; }
+static int64_t fused_ar_header(int64_t max_n_total) { return (4 * fused_ar_units(max_n_total) + 4095) & ~(int64_t)4095; }
 
 extern "C" int64_t gq_fused_allreduce_buffer_bytes(int world, int64_t max_m, int64_t max_n_total) {
     if (world < 1 || world > GQ_AR_MAX_WORLD || max_m < 1 || max_m > GQ_MAX_GEMV_ROWS || max_n_total < 1) return GQ_ERR_ARG;
-    return fused_ar_header(world, max_n_total) + 2 * (int64_t)world * align256(max_m * max_n_total * 2);
+    return fused_ar_header(max_n_total) + 2 * (int64_t)world * align256(max_m * max_n_total * 4);
 }
 
 extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
@@ -1070,12 +1046,12 @@ extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K
     if (max_m < 1 || max_m > GQ_MAX_GEMV_ROWS || M > max_m || n_total > max_n_total) return GQ_ERR_SHAPE;
     ArFused ar = {};
     ar.world = world; ar.rank = rank; ar.units = (int)fused_ar_units(max_n_total);
-    ar.slot_bytes = align256(max_m * max_n_total * 2);
-    const int64_t header = fused_ar_header(world, max_n_total);
+    if (n_total & 1) return GQ_ERR_SHAPE;
+    ar.slot_bytes = align256(max_m * max_n_total * 4);
+    const int64_t header = fused_ar_header(max_n_total);
     for (int p = 0; p < world; ++p) {
         if (!peer_buffers[p] || (peer_buffers[p] & 255)) return GQ_ERR_ARG;
         uint8_t *b = reinterpret_cast<uint8_t *>(peer_buffers[p]);
-        ar.flags[p] = reinterpret_cast<uint32_t *>(b) + ar.units;
         ar.buf[p] = b + header;
     }
     ar.counters = reinterpret_cast<uint32_t *>(peer_buffers[rank]);

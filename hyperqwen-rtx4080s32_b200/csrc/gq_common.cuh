@@ -17,6 +17,7 @@
 #define GQ_ERR_LIMIT (-6)
 // device status word values (positive)
 #define GQ_DEV_TIMEOUT 1
+#define GQ_DEV_BAD_SHAPE 2
 
 #define GQ_SPIN_LIMIT (1u << 30)   // polls of a try_wait loop before a kernel gives up and reports GQ_DEV_TIMEOUT (the time limit ends it first)
 

@@ -289,7 +289,7 @@ def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[tor
         if s not in desc_splits:
             s = 1
         ar = _FUSED_AR
-        if ar is not None and not (m <= ar.max_m and n_total <= ar.max_n_total and s <= 8):
+        if ar is not None and not (m <= ar.max_m and n_total <= ar.max_n_total and s <= 8 and all(int(n) % 2 == 0 for n in n_outs)):
             ar = None
         grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, out=out, allreduce=ar)
         return out

@@ -164,15 +164,16 @@ int gq_allreduce_push(const void *in_dev, void *out_dev, int64_t n_bytes, int ra
 
 /* gq_gemv_grouped fused with the all-reduce of a row-parallel layer: every rank passes its K shard of x and of
  * the weights; on return (in stream order) y holds the sum over ranks of the ranks' bf16 partial outputs, on
- * every rank.  The exchange happens in the kernel's epilogue, per 16 output columns: a warp pushes its block into
- * its rank's slot of every rank's buffer (plain stores through peer pointers), publishes a flag, waits with a time
- * limit for the same block of the other ranks (a timeout sets the workspace's status word) and sums the slots
- * from its own memory in rank order — the arithmetic of gq_gemv_grouped followed by gq_allreduce_push, without the
- * second launch.  peer_buffers[p] is rank p's buffer of gq_fused_allreduce_buffer_bytes(world, max_m,
- * max_n_total) bytes as seen from this process (peer-mapped, 256-byte aligned, zeroed once before the first
- * call); M <= max_m, n_total <= max_n_total; split must be 1 or reduce inside the kernel (<= 8); every rank makes
- * the same sequence of calls on a buffer.  No loads from remote memory, no multicast.
- * Reference: none — the reference has no collective on this path (docs/multi-gpu.md:8-13). */
+ * every rank.  The exchange happens in the kernel's epilogue, per 16 output columns: a warp stores its block into
+ * its rank's slot of every rank's buffer (plain stores through peer pointers) as 8-byte words {two bf16 values,
+ * call number}; the receiver polls the words of its own memory until they carry this call's number (with a time
+ * limit: a timeout sets the workspace's status word to 1) and sums them in rank order — the arithmetic of
+ * gq_gemv_grouped followed by gq_allreduce_push, without the second launch and without fences at system scope.
+ * peer_buffers[p] is rank p's buffer of gq_fused_allreduce_buffer_bytes(world, max_m, max_n_total) bytes as seen
+ * from this process (peer-mapped, 256-byte aligned, zeroed once before the first call); M <= max_m, n_total <=
+ * max_n_total; n_total and every shard's n_out even (status word 2 otherwise); split must be 1 or reduce inside
+ * the kernel (<= 8); every rank makes the same sequence of calls on a buffer.  No loads from remote memory, no
+ * multicast.  Reference: none — the reference has no collective on this path (docs/multi-gpu.md:8-13). */
 int64_t gq_fused_allreduce_buffer_bytes(int world, int64_t max_m, int64_t max_n_total);
 int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
                               int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
