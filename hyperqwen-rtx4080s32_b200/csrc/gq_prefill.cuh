@@ -87,9 +87,12 @@ __device__ __forceinline__ void pf_store_pair(const Dec<TYPE> &dec, uint8_t *a_s
             if constexpr (off != 0.0f) { w01 = hsub2(w01, h2k(off)); w23 = hsub2(w23, h2k(off)); }
             if constexpr (Dec<TYPE>::HAS_MIN) { w01 = hfma2(w01, sc[h], mn[h]); w23 = hfma2(w23, sc[h], mn[h]); }
             else { w01 = hmul2(w01, sc[h]); w23 = hmul2(w23, sc[h]); }
-            const int row = row0 + g + 8 * h;
+            // A-tile row of weight row g + 8h of the slab: 2g + h.  Interleaving the two rows a lane owns gives the
+            // sixteen lanes of a half-warp (g = 0..3 or 4..7, one h) four different swizzle phases, so their 8-byte
+            // stores hit all 32 banks once; with row = g + 8h rows g and g + 8 shared a phase (2-way conflicts)
+            const int row = row0 + 2 * g + h;
             const int chunk = chunk0 + 2 * u + (t >> 1);
-            uint8_t *dst = a_stage + row * 128 + ((chunk ^ g) << 4) + ((t & 1) << 3);
+            uint8_t *dst = a_stage + row * 128 + ((chunk ^ (row & 7)) << 4) + ((t & 1) << 3);
             *reinterpret_cast<uint2 *>(dst) = make_uint2(w01, w23);
         }
     }
@@ -249,7 +252,8 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, 1) gemm_prefill_kernel(const Pr
             const int lg = warp & 3, half = (warp - 2) >> 2;
             const int feat = 32 * lg + lane;                       // row of the 128-row tile pair
             const int32_t *dt = (feat < 64) ? d0 : d1;
-            const int r = feat & 63;
+            const int ra = feat & 63;                              // row of the A tile -> weight row of the packed tile
+            const int r = (ra & ~15) | ((ra & 15) >> 1) | ((ra & 1) << 3);
             const bool row_ok = (feat < 64 || has1) && r < dt[3];
             const int64_t col = (int64_t)dt[2] + r;
 #pragma unroll 1
