@@ -178,6 +178,24 @@ def run_ours(args):
     fused = world > 1 and not args.nccl_allreduce and not args.unfused_allreduce and args.m <= 64
     if fused:
         st.enable_fused_all_reduce(max_m=64)
+        # the fused exchange must reproduce the separate all-reduce bit for bit on this process group before it is
+        # timed; if any rank sees a difference the run falls back to the separate push kernel and says so
+        from hyperqwen_rtx4080s32_b200 import tp as _tp
+
+        xin = st.make_inputs(args.m)
+        lin = st.layers[0]["o"]
+        want = lin(xin["o"]).clone()
+        _tp.all_reduce_(want)
+        st.fused_ar.used = False
+        with ops.fused_allreduce(st.fused_ar):
+            got = lin(xin["o"])
+        torch.cuda.synchronize()
+        same = torch.tensor([1 if (st.fused_ar.used and torch.equal(got, want)) else 0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        if int(same.item()) == 0:
+            print(f"[rank {rank}] fused all-reduce self-check failed: using the separate push kernel", file=sys.stderr, flush=True)
+            st.fused_ar = None
+            fused = False
     m = args.m
     st.enable_prefetch(args.l2_prefetch and not args.no_l2_prefetch)
     x_dev = st.make_inputs(m)
