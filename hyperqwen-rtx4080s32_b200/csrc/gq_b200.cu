@@ -542,7 +542,9 @@ __device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const ui
 // registers, which it turns into more loads and MMAs in flight per warp: measured 14 % faster than the 72-register
 // build when a CTA walks ten or more k-blocks, a little slower on launches of many short CTAs, 2 % faster on the
 // mixed stack.  (Compiling both and choosing per call was slower than either alone: alternating between two large
-// kernels costs more in instruction-cache misses at every launch than the better fit gains.)
+// kernels costs more in instruction-cache misses at every launch than the better fit gains.)  The 17..32-row form
+// is about 10 % faster with room for two CTAs (168 registers) than with the compiler's own 144; the 16- and 64-row
+// forms were best left alone.
 template <int MT, int MINB>
 __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_grouped_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -958,7 +960,7 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         switch (mt) {
             case 1: rc = launch_gemv<1, 4>(p, n_desc, st); break;
             case 2: rc = launch_gemv<2, 0>(p, n_desc, st); break;
-            case 4: rc = launch_gemv<4, 0>(p, n_desc, st); break;
+            case 4: rc = launch_gemv<4, 2>(p, n_desc, st); break;
             default: rc = launch_gemv<8, 0>(p, n_desc, st); break;
         }
     }
