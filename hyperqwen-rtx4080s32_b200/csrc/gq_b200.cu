@@ -367,6 +367,7 @@ struct GemvParams {
     int wbytes_max;      // largest tile bytes in the launch (stage stride of the weight buffers)
     int has_iq3s;
     int cluster;         // 1: the `split` CTAs of a tile form a thread-block cluster and reduce through shared memory
+    int cluster_push;    // 1: the others store their accumulators into slots of the split-0 CTA's shared memory (one cluster barrier)
     const uint8_t *pf_ptr;   // weights the caller will multiply next (or null): prefetched into L2 while this launch computes
     int64_t pf_bytes;
     ArFused ar;
@@ -611,8 +612,8 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             }
         }
         if (!p.cluster) return;
-        cluster_sync_all();     // the reduction's two cluster barriers need every thread of every CTA
-        cluster_sync_all();
+        cluster_sync_all();     // the reduction's cluster barriers need every thread of every CTA
+        if (!p.cluster_push) cluster_sync_all();
         return;
     }
 
@@ -647,10 +648,31 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     const int g = lane >> 2, t = lane & 3;
     // scratch of its own behind the ring (a slower warp may still read the ring): GQ_CONSUMER_WARPS x MT x 512 bytes
     float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0));
-    if (p.cluster) {
-        // split-K inside a cluster: every CTA parks its accumulators in its own shared memory (the stage ring is
-        // idle by now), the CTA of split 0 adds the others' in split order through distributed shared memory and
-        // writes bf16 once.  No partial sums in HBM, no second kernel; the order of the additions is fixed.
+    if (p.cluster && p.cluster_push) {
+        // split-K inside a cluster, push form: the CTAs of splits 1.. store their accumulators into their slot of the
+        // split-0 CTA's scratch through distributed shared memory; one cluster barrier (release / acquire) later that
+        // CTA adds the slots from its own shared memory, in split order, and writes bf16 once.  No partial sums in
+        // HBM, no second kernel, fixed order of the additions.
+        if (split_idx != 0) {
+            const uint32_t dst = map_to_rank(smem_u32(red), 0u) + (uint32_t)((split_idx - 1) * GQ_CONSUMER_WARPS * MT * 512);
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt)
+                st_cluster_f4(dst + (uint32_t)(((warp * MT + nt) * 32 + lane) * 16), acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+        }
+        cluster_sync_all();
+        if (split_idx != 0) return;
+        for (int s = 1; s < p.split; ++s) {
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt) {
+                const float4 v = red[((s - 1) * GQ_CONSUMER_WARPS * MT + warp * MT + nt) * 32 + lane];
+                acc[nt][0] += v.x; acc[nt][1] += v.y; acc[nt][2] += v.z; acc[nt][3] += v.w;
+            }
+        }
+        __syncwarp();       // the warp's part of slot 0 becomes its scratch again below
+    } else if (p.cluster) {
+        // pull form (when the slots do not fit without costing a resident CTA): every CTA parks its accumulators in
+        // its own shared memory, the CTA of split 0 adds the others' in split order through distributed shared
+        // memory between two cluster barriers
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt) red[(warp * MT + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
         cluster_sync_all();
@@ -852,7 +874,8 @@ template <int MT, int MINB>
 static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream) {
     const int xbytes = 8 * MT * GQ_XROW_BYTES;
     const int stage_bytes = p.wbytes_max + xbytes;
-    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) + (size_t)GQ_CONSUMER_WARPS * MT * 512;
+    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) +
+                        (size_t)GQ_CONSUMER_WARPS * MT * 512 * (p.cluster_push ? p.split - 1 : 1);
     // opt in once per device to the largest dynamic shared memory any launch of this variant can ask for
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
@@ -935,6 +958,12 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     // split-K up to 8 reduces inside a thread-block cluster (portable cluster size); larger splits keep the fp32
     // partials and the separate sum
     p.cluster = (split > 1 && split <= 8 && n_desc % split == 0) ? 1 : 0;
+    {
+        static int no_cluster = -1;   // tuning knob: GQ_NO_CLUSTER=1 sends every split through the fp32 partials instead
+        if (no_cluster < 0) { const char *e = getenv("GQ_NO_CLUSTER"); no_cluster = (e && e[0] == '1') ? 1 : 0; }
+        if (no_cluster) p.cluster = 0;
+    }
+    p.cluster_push = 0;
     p.pf_ptr = (next_packed_dev && next_bytes > 0 && !((uintptr_t)next_packed_dev & 15)) ? (const uint8_t *)next_packed_dev : nullptr;
     p.pf_bytes = next_bytes;
     if (ar) {
@@ -950,7 +979,17 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         // 64-layer stack: deeper rings with fewer resident CTAs were slower overall)
         const int stage_bytes = p.wbytes_max + 8 * mt * GQ_XROW_BYTES;
         // (an SM has 228 KB of shared memory and the system keeps 1 KB of it per resident CTA)
-        p.stages = (4 * (4 * stage_bytes + 64 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) + GQ_CONSUMER_WARPS * mt * 512 + 1024) <= 228 * 1024) ? 4 : 3;
+        const int fixed = 64 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) + 1024, red1 = GQ_CONSUMER_WARPS * mt * 512;
+        // split-K in a cluster: the push form of the reduction needs a scratch slot per other split in every CTA; it
+        // is used when that costs no resident CTA (the ring then has three stages; its depth does not matter)
+        p.cluster_push = 0;
+        if (p.cluster) {
+            const int pull = (228 * 1024) / (3 * stage_bytes + fixed + red1), push = (228 * 1024) / (3 * stage_bytes + fixed + red1 * (split - 1));
+            const int cap = mt == 1 ? 4 : 8;     // resident CTAs the register budget allows anyway
+            p.cluster_push = (push > cap ? cap : push) >= (pull > cap ? cap : pull) ? 1 : 0;
+        }
+        const int red = p.cluster_push ? red1 * (split - 1) : red1;
+        p.stages = (4 * (4 * stage_bytes + fixed + red) <= 228 * 1024) ? 4 : 3;
         static int forced = -1;   // tuning knob: GQ_STAGES=n overrides the ring depth
         if (forced < 0) { const char *e = getenv("GQ_STAGES"); forced = e ? atoi(e) : 0; }
         if (forced >= 2 && forced <= 8) p.stages = forced;
