@@ -84,6 +84,30 @@ def test_split_policy_bounds(gq_lib):
         assert 1 <= s <= nb
 
 
+def test_split_policy_on_the_decoder_shapes(gq_lib):
+    """148 SMs, four CTAs per SM: the largest split that leaves three k-blocks per CTA, fits a cluster of 8 and keeps
+    the launch in one wave with headroom for cluster placement."""
+    got = {name: gq_lib.gq_split_for(tiles, nb, 8, 144, 148)
+           for name, tiles, nb in [("q", 80, 20), ("qkv", 112, 20), ("gate", 272, 20), ("gate_up", 544, 20), ("down", 80, 68), ("kv", 16, 20)]}
+    assert got == {"q": 6, "qkv": 4, "gate": 2, "gate_up": 1, "down": 6, "kv": 6}
+
+
+def test_fused_allreduce_buffer_size_and_argument_checks(gq_lib):
+    b2 = gq_lib.gq_fused_allreduce_buffer_bytes(2, 64, 5120)
+    b8 = gq_lib.gq_fused_allreduce_buffer_bytes(8, 64, 5120)
+    # a header of per-(tile, warp) call counters, then two slot sets of `world` images of 8-byte words per bf16 pair
+    assert b2 % 256 == 0 and b8 - b2 == 2 * 6 * 64 * 5120 * 4
+    assert gq_lib.gq_fused_allreduce_buffer_bytes(0, 64, 5120) < 0 and gq_lib.gq_fused_allreduce_buffer_bytes(9, 64, 5120) < 0
+    assert gq_lib.gq_fused_allreduce_buffer_bytes(2, 65, 5120) < 0 and gq_lib.gq_fused_allreduce_buffer_bytes(2, 8, 0) < 0
+    # rejected on the host before anything touches a device: no peers, rank out of range, batch above the buffers'
+    peers = (ctypes.c_uint64 * 2)(0, 0)
+    args = [None, 8, 256, 256, None, None, 1, 1, 144, None, 64, 64, None, 0]
+    assert gq_lib.gq_gemv_grouped_allreduce(*args, 0, 2, None, 64, 64, None) == -3
+    assert gq_lib.gq_gemv_grouped_allreduce(*args, 2, 2, peers, 64, 64, None) == -3
+    args[1] = 65
+    assert gq_lib.gq_gemv_grouped_allreduce(*args, 0, 2, peers, 64, 64, None) == -2
+
+
 def test_build_descs_rejects_bad_arguments(gq_lib):
     n = (ctypes.c_int64 * 1)(64)
     buf = (ctypes.c_int32 * 64)()
