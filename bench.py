@@ -177,7 +177,17 @@ def run_ours(args):
     st = S.LinearStack(n_layers=args.layers, device=dev, tp_rank=rank, tp_size=world)
     fused = world > 1 and not args.nccl_allreduce and not args.unfused_allreduce and args.m <= 64
     if fused:
-        st.enable_fused_all_reduce(max_m=64)
+        try:
+            st.enable_fused_all_reduce(max_m=64)
+        except Exception as e:      # no peer-mapped memory on this box: the separate all-reduce still works
+            print(f"[rank {rank}] fused all-reduce unavailable ({e}): using the separate all-reduce", file=sys.stderr, flush=True)
+            st.fused_ar = None
+        ready = torch.tensor([1 if getattr(st, "fused_ar", None) is not None else 0], device=dev)
+        dist.all_reduce(ready, op=dist.ReduceOp.MIN)
+        if int(ready.item()) == 0:
+            st.fused_ar = None
+            fused = False
+    if fused:
         # the fused exchange must reproduce the separate all-reduce bit for bit on this process group before it is
         # timed; if any rank sees a difference the run falls back to the separate push kernel and says so
         from hyperqwen_rtx4080s32_b200 import tp as _tp
