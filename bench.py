@@ -98,6 +98,7 @@ def cpu_sample(m: int, n_layers: int, target_s: float = 0.0):
     from hyperqwen_rtx4080s32_b200 import synth
     from oracle import oracle
 
+    oracle.use_all_cores()
     types = S.draw_types(64)[:n_layers]
     shapes = {"q": (5120, 5120), "k": (1024, 5120), "v": (1024, 5120), "o": (5120, 5120), "gate": (17408, 5120),
               "up": (17408, 5120), "down": (5120, 17408)}
@@ -131,6 +132,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from oracle import oracle
+
+    oracle.use_all_cores()
     vals = []
     for _ in range(min(args.warmup, 1)):
         cpu_sample(args.m, 1)

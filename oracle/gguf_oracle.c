@@ -327,6 +327,11 @@ int oracle_matmul(int type, const uint8_t *raw, int64_t n_rows, int64_t K, const
     return 0;
 }
 
+/* threads the OpenMP loops use from now on (a launcher may have exported OMP_NUM_THREADS=1 for its workers) */
+void oracle_set_num_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -111,6 +111,19 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def use_all_cores() -> int:
+    """Let the OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS says (torchrun
+    exports OMP_NUM_THREADS=1 to its workers); returns the thread count now in force."""
+    import os
+
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    L = lib()
+    L.oracle_set_num_threads.argtypes = [ctypes.c_int]
+    L.oracle_set_num_threads.restype = None
+    L.oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 def rel_err(y, y_ref) -> float:
     """max over rows and columns of |y - y_ref| / (that row's max |y_ref|) for y [M, n] — the
     reference's error metric."""
