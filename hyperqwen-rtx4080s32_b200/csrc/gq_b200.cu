@@ -573,6 +573,11 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]);
     }
     __syncthreads();
+    // push-form split-K: a CTA may store into the split-0 CTA's shared memory only once that CTA is known to run;
+    // every thread enters this rendezvous here and collects it just before its first remote store (or before the
+    // closing barrier), long after everyone has arrived
+    const bool push = p.cluster && p.cluster_push;
+    if (push) cluster_arrive_relaxed();
 
     if (warp == GQ_CONSUMER_WARPS) {
         // ---- producer: one thread; per k-block one bulk copy of the weight tile and one of the activation tile.
@@ -612,8 +617,9 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             }
         }
         if (!p.cluster) return;
+        if (push) cluster_wait();
         cluster_sync_all();     // the reduction's cluster barriers need every thread of every CTA
-        if (!p.cluster_push) cluster_sync_all();
+        if (!push) cluster_sync_all();
         return;
     }
 
@@ -648,7 +654,8 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     const int g = lane >> 2, t = lane & 3;
     // scratch of its own behind the ring (a slower warp may still read the ring): GQ_CONSUMER_WARPS x MT x 512 bytes
     float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0));
-    if (p.cluster && p.cluster_push) {
+    if (push) {
+        cluster_wait();         // the rendezvous entered at the start: every CTA of the cluster is running
         // split-K inside a cluster, push form: the CTAs of splits 1.. store their accumulators into their slot of the
         // split-0 CTA's scratch through distributed shared memory; one cluster barrier (release / acquire) later that
         // CTA adds the slots from its own shared memory, in split order, and writes bf16 once.  No partial sums in
