@@ -17,7 +17,7 @@ layer.gguf_tiles_types, layer.gguf_groups.  Shard ids are "q","k","v" for a fuse
 order is forced) and 0, 1 for gate_up.
 
 It does not import vLLM: `layer` is any torch.nn.Module.  Inside vLLM the class is used as the
-`LinearMethodBase` returned by the `gguf` QuantizationConfig (INTEGRATION.md shows the binding).
+`LinearMethodBase` returned by the `gguf` QuantizationConfig.
 """
 from __future__ import annotations
 

@@ -23,7 +23,9 @@ sys.path.insert(0, ROOT)
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference repository>")
+    ref_root = sys.argv[1]
     from gguf.constants import GGMLQuantizationType as GT
     from gguf.quants import dequantize
 
