@@ -1,5 +1,5 @@
 """Generates tests/golden/dequant_golden.npz — run in a container that has the reference checkout and
-the gguf package:  python tests/golden/make_golden.py [/path/to/reference]
+the gguf package:  python tests/golden/make_golden.py <path to the reference checkout>
 
 Two families of golden vectors for the oracle (oracle/gguf_oracle.c):
   * gguf_<TYPE>_raw / gguf_<TYPE>_w : random valid blocks of each of the eleven types (seeded, our own
