@@ -21,7 +21,8 @@ from ._lib import DESC_WORDS, MAX_GEMV_ROWS, GqError, check, lib
 
 TILE_TYPES = F.SUPPORTED_TYPES   # every one of the eleven types is held tile-major (the reference: GLUON_TILE_TYPES)
 GEMV_MAX_ROWS = MAX_GEMV_ROWS    # row-count dispatch threshold: above it the prefill kernel takes over
-WIDE_MIN_ROWS = 32               # ... and above this one already, when the run has at least two tiles per SM
+WIDE_MIN_ROWS = 32               # above it the small-batch path runs as two launches of at most 32 rows
+WIDE_PREFILL_ROWS = 40           # ... and above this one a run of at least two tiles per SM goes to the prefill kernel already
 
 
 def _stream_ptr(t: torch.Tensor) -> int:
@@ -272,7 +273,7 @@ def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[tor
     """A layer's run of shards in one call: x bf16 [M, K] -> [M, sum(n_outs)] (reference:
     gluon_mul_mat_tiles_grouped, gguf-plugin/gluon/interface.py:141-188).  The row-count dispatch lives
     here, inside the op: up to 64 rows one grouped launch at the split of the table for that row count
-    (up to 32 rows for runs of at least two tiles per SM); above, the tcgen05 dequant-GEMM (weights
+    (33..64 rows as two launches; up to 40 rows for runs of at least two tiles per SM); above, the tcgen05 dequant-GEMM (weights
     dequantised into shared memory once per 256 batch rows)."""
     m = int(x.shape[0])
     n_total = sum(int(n) for n in n_outs)
@@ -280,10 +281,10 @@ def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[tor
     if m == 0:
         return out
     n_tiles = sum(-(-int(n) // 64) for n in n_outs)
-    # 33..64 rows: the grouped kernel re-reads a 39 KB activation tile per k-block and CTA there and is bound by
-    # that; a run wide enough to give every SM a CTA of the tcgen05 kernel (two tiles each) is faster on it
-    # (gate_up at 48-64 rows: 110 vs 140 us)
-    wide = m > WIDE_MIN_ROWS and n_tiles >= 2 * sm_count(x.device)
+    # 41..64 rows: a run wide enough to give every SM a CTA of the tcgen05 kernel (two tiles each) is faster on it
+    # than on the grouped kernel (gate_up: 110 us against 116 us for two 32-row launches, 140 us for one 64-row launch;
+    # measured on the mixed stack: the grouped kernel wins at 33 rows, the tcgen05 kernel at 48)
+    wide = m > WIDE_PREFILL_ROWS and n_tiles >= 2 * sm_count(x.device)
     if m <= GEMV_MAX_ROWS and not wide:
         s = grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=sm_count(x.device))
         if s not in desc_splits:
@@ -291,7 +292,16 @@ def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[tor
         ar = _FUSED_AR
         if ar is not None and not (m <= ar.max_m and n_total <= ar.max_n_total and s <= 8 and all(int(n) % 2 == 0 for n in n_outs)):
             ar = None
-        grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, out=out, allreduce=ar)
+        d = descs[desc_splits.index(s)]
+        if m > WIDE_MIN_ROWS:
+            # 33..64 rows: 32 rows and the rest in two launches beat one launch of the 64-row form (whose 39 KB
+            # activation tile per k-block leaves one CTA per SM); the second pass finds most of the weights in L2.
+            # Rows are independent, so the result is the same either way.
+            h = WIDE_MIN_ROWS
+            grouped_gemm(x[:h], packed, d, s, weight_types, n_total, out=out[:h], allreduce=ar)
+            grouped_gemm(x[h:], packed, d, s, weight_types, n_total, out=out[h:], allreduce=ar)
+            return out
+        grouped_gemm(x, packed, d, s, weight_types, n_total, out=out, allreduce=ar)
         return out
     prefill_gemm(x, packed, descs[desc_splits.index(1)], n_total, out=out)
     return out
