@@ -13,8 +13,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB = os.path.join(_HERE, "libgq_b200.so")
 SOURCES = ["gq_b200.cu"]
-HEADERS = ["gq_common.cuh", "gq_decode.cuh", "gq_layout.h", os.path.join("..", "..", "include", "gq_b200.h")]
-NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--expt-relaxed-constexpr",
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) + [os.path.join("..", "..", "include", "gq_b200.h")]
+NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--expt-relaxed-constexpr", "-diag-suppress", "177",
               "-shared", "-Xcompiler", "-fPIC"]
 
 

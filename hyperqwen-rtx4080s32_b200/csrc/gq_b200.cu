@@ -7,6 +7,8 @@
 #include <atomic>
 #include "../../include/gq_b200.h"
 #include "gq_decode.cuh"
+#include "gq_decode8.cuh"
+#include <type_traits>
 #include "_generated/gq_tables.h"
 
 using namespace gq;
@@ -211,10 +213,24 @@ struct Workspace {
 
 __host__ __device__ inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 
+// The same row in the integer form used for 1..16 batch rows: per k-block and batch row the activations as 16-bit
+// fixed point (x * 2^e, e chosen per row and k-block so that the largest magnitude lands in [2^14, 2^15)), split into
+// a signed high-byte plane (256 B) and an unsigned low-byte plane (256 B), then the sixteen 16-weight run sums
+// (times 2^-6) as fp16 hi parts (32 B) and lo parts (32 B).  Inside a plane the bytes are ordered for the lane that
+// reads them: 16-byte unit 4*i + t holds, for runs 4i..4i+3, the quad 4t..4t+3 with bytes in the order (0,2,1,3).
+// 576 = 64 mod 128, so the two rows a quarter-warp reads with one 16-byte load each sit in different banks.
+// After the rows of a k-block come their scales 2^-e (fp32, one per batch row, padded to a multiple of 16 bytes).
+#define GQ_X8_ROW 576
+#define GQ_X8_SUMS 512
+#define GQ_GEMV8_MAX_ROWS 16      // up to here the integer form runs; above it the fp16 form
+
+__host__ __device__ inline int gq_x8_tile_bytes(int M) { return M * GQ_X8_ROW + ((4 * M + 15) & ~15); }
+
 static int64_t ws_layout(int64_t M, int64_t K, int64_t n_total, int split, void *base, Workspace *ws) {
     int64_t off = 256;
     const int64_t o_ex = off; off = align256(off + M * 4);
-    const int64_t o_xt = off; off = align256(off + (K / GQ_QK) * M * GQ_XROW_BYTES);
+    const int64_t xt_bytes = M <= GQ_GEMV8_MAX_ROWS ? (K / GQ_QK) * gq_x8_tile_bytes((int)M) : (K / GQ_QK) * M * GQ_XROW_BYTES;
+    const int64_t o_xt = off; off = align256(off + xt_bytes);
     const int64_t o_p = off; if (split > 1) off = align256(off + (int64_t)split * M * n_total * 4);
     if (ws && base) {
         uint8_t *b = (uint8_t *)base;
@@ -331,6 +347,78 @@ __global__ void __launch_bounds__(GQ_PREP_THREADS) prep_x_kernel(const __nv_bflo
             prep_store8(t, idx, scale, M, m, xt);
         }
     }
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// activation preparation, integer form (1..16 batch rows): one warp per (batch row, k-block).  The 256 activations
+// become 16-bit fixed point at a power-of-two scale of their own (exact for every value within 2^-7 of the block's
+// largest magnitude, rounded to 2^-16 of it below), stored as the two byte planes, the run sums and the scale
+// described at GQ_X8_ROW.  Plays the role of the reference's quantize_activations_256
+// (gguf-plugin/gluon/tiles_grouped.py:110-139), which keeps 8 bits per activation; this keeps 16.
+// ---------------------------------------------------------------------------------------------------
+#define GQ_PREP8_WARPS 8
+
+__global__ void __launch_bounds__(32 * GQ_PREP8_WARPS) prep_x8_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int M, uint8_t *__restrict__ xt,
+                                                                      int *status) {
+    const int lane = threadIdx.x & 31, kb = blockIdx.x;
+    const int m = blockIdx.y * GQ_PREP8_WARPS + (threadIdx.x >> 5);
+    pdl_trigger();    // the grouped kernel behind this one may start fetching weights
+    pdl_wait();       // whatever ran before (possibly still reading this workspace) has finished
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *status = 0;
+    if (m >= M) return;
+    const __nv_bfloat16 *xr = x + (int64_t)m * ldx + (int64_t)kb * GQ_QK + 8 * lane;
+    float v[8];
+    if ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xr));
+        const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(xr[j]);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bad |= !(fabsf(v[j]) <= 3.0e38f);      // NaN or infinity
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    bad = __any_sync(0xffffffffu, bad);
+    // scale = 2^(14 - e) with 2^e <= amax < 2^(e+1); a zero block keeps scale 1; a block holding a NaN or an infinity
+    // gets a NaN scale, so that every output of that batch row is NaN as it would be in floating point
+    int e = 14;
+    if (amax > 0.0f) { e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127; if (e < -100) e = -100; }
+    const float scale = __uint_as_float((uint32_t)(127 + 14 - e) << 23);
+    const float inv = bad ? __uint_as_float(0x7fc00000u) : __uint_as_float((uint32_t)(127 - 14 + e) << 23);
+    int xi[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { xi[j] = bad ? 0 : __float2int_rn(v[j] * scale); sum += xi[j]; }
+    uint8_t *row = xt + (int64_t)kb * gq_x8_tile_bytes(M) + (int64_t)m * GQ_X8_ROW;
+    // this lane holds quads 2*(lane & 1) and 2*(lane & 1) + 1 of run lane >> 1
+    const int r = lane >> 1, tq = 2 * (lane & 1);
+#pragma unroll
+    for (int qd = 0; qd < 2; ++qd) {
+        const int *q = xi + 4 * qd;
+        const uint32_t hi = ((uint32_t)(q[0] >> 8) & 0xFFu) | (((uint32_t)(q[2] >> 8) & 0xFFu) << 8) | (((uint32_t)(q[1] >> 8) & 0xFFu) << 16) |
+                            (((uint32_t)(q[3] >> 8) & 0xFFu) << 24);
+        const uint32_t lo = ((uint32_t)q[0] & 0xFFu) | (((uint32_t)q[2] & 0xFFu) << 8) | (((uint32_t)q[1] & 0xFFu) << 16) | (((uint32_t)q[3] & 0xFFu) << 24);
+        const int off = 64 * (r >> 2) + 16 * (tq + qd) + 4 * (r & 3);
+        *reinterpret_cast<uint32_t *>(row + off) = hi;
+        *reinterpret_cast<uint32_t *>(row + 256 + off) = lo;
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    if (!(lane & 1)) {
+        const float f = (float)sum * 0.015625f;          // exact: |sum| < 2^20
+        const __half hi = __float2half_rn(f);
+        const __half lo = __float2half_rn(f - __half2float(hi));
+        __half *so = reinterpret_cast<__half *>(row + GQ_X8_SUMS);
+        so[r] = hi;
+        so[16 + r] = lo;
+    }
+    if (lane == 0) *reinterpret_cast<float *>(xt + (int64_t)kb * gq_x8_tile_bytes(M) + (int64_t)M * GQ_X8_ROW + 4 * m) = inv;
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -459,19 +547,222 @@ __device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *
     }
 }
 
+#ifdef GQ_TRACE
+__device__ long long g_trace[1024 * 64 * 4];
+__device__ unsigned long long g_tl[1024 * 8];    // per CTA wall-clock marks (ns): entry, prologue end, pdl wait end, first data, loop end, exit
+extern "C" int gq_trace_read(long long *host) { return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof g_trace); }
+extern "C" int gq_timeline_read(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, g_tl, sizeof g_tl); }
+#define GQ_MARK(k) do { if (blockIdx.x < 1024) g_tl[blockIdx.x * 8 + (k)] = global_timer_ns(); } while (0)
+#else
+#define GQ_MARK(k) do { } while (0)
+#endif
+
+// The stage ring of one CTA: per stage the weight tile of one k-block and the matching activation tile, filled by two
+// bulk copies that complete on the stage's "full" mbarrier; the four consumer warps hand a stage back through its
+// "empty" mbarrier, on which the producer warp waits before it refills the stage.  (Letting the last consumer warp to
+// finish a stage issue the refill itself — no producer warp, nobody polling — was measured 15 % slower: the arrival
+// whose returned state tells a warp that it is the last one, and the copy issue behind it, then sit on the consumer's
+// critical path every k-block.)
+struct Ring {
+    uint8_t *smem;
+    uint64_t *full, *empty;
+    int stages, stage_bytes, wmax, nk;
+};
+
 // the consumer loop of one warp for a CTA whose shard is of TYPE: waits for each stage, processes its slab,
 // releases the stage.  Returns false if a bounded wait ran out.
 template <int TYPE, int MT>
-__device__ __forceinline__ bool consume(const uint8_t *smem, uint64_t *full, uint64_t *empty, int stages, int stage_bytes, int wmax,
-                                        int slab_off, int nk, const DecAux &aux, int lane, float (&acc)[MT][4]) {
+__device__ __forceinline__ bool consume(const Ring &r, int slab_off, const DecAux &aux, int lane, float (&acc)[MT][4]) {
     float z[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int i = 0, s = 0, round = 0; i < nk; ++i) {
-        if (!mbar_wait(full + s, round & 1)) return false;
-        const uint8_t *st = smem + (size_t)s * stage_bytes;
-        slab_kblock<TYPE, MT>(st + slab_off, st + wmax, aux, lane, acc, z);
+    for (int i = 0, s = 0, round = 0; i < r.nk; ++i) {
+        if (!mbar_wait(r.full + s, round & 1)) return false;
+        const uint8_t *st = r.smem + (size_t)s * r.stage_bytes;
+        slab_kblock<TYPE, MT>(st + slab_off, st + r.wmax, aux, lane, acc, z);
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty + s);
-        if (++s == stages) { s = 0; ++round; }
+        if (lane == 0) mbar_arrive(r.empty + s);
+        if (++s == r.stages) { s = 0; ++round; }
+    }
+    return true;
+}
+
+
+// ---- integer form (1..16 batch rows): mma.sync m16n8k32 / m16n8k16 on 8-bit operands ----------------------
+// D (int32, 16 x 8) = A (16 weight rows x 32 k, 8-bit) . B (32 k x 8 batch rows, 8-bit) [+ C].  AS / BS: operand is signed.
+template <bool AS, bool BS>
+__device__ __forceinline__ void imma32(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, int c0, int c1, int c2, int c3) {
+    if constexpr (AS && BS)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+    else if constexpr (AS && !BS)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+    else if constexpr (!AS && BS)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+    else
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+template <bool AS, bool BS>
+__device__ __forceinline__ void imma16(int (&d)[4], const uint32_t (&a)[2], uint32_t b0) {
+    if constexpr (AS && BS)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(b0), "r"(0));
+    else if constexpr (AS && !BS)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(b0), "r"(0));
+    else if constexpr (!AS && BS)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(b0), "r"(0));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(b0), "r"(0));
+}
+
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F &&f) {
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
+}
+
+// one k-block of one slab in the integer form.  `xs` is the staged activation tile of the k-block (rows of GQ_X8_ROW
+// bytes, then the batch rows' scales at xs_off).  Per MMA the weights are 8-bit integers and the activations one of the
+// two byte planes (x = 256 hi + lo with hi signed, lo unsigned); int32 sums per plane are exact.  At the end of the
+// k-block:  acc += 2^-e[n] * ( d[row] * (256 sumH + sumL) - f[row] * 64 * sum_run A''[row][run] * Sx[run][n] ).
+template <int TYPE, int MT>
+__device__ __forceinline__ void slab_kblock8(const uint8_t *slab, const uint8_t *xs, int xs_off, const DecAux8 &aux, int lane, float (&acc)[MT][4]) {
+    using D = Dec8<TYPE>;
+    constexpr bool AS = D::A_SIGNED;
+    D dec;
+    dec.load(slab, lane, aux);
+    const int g = lane >> 2, t = lane & 3;
+    const uint8_t *xb = xs + g * GQ_X8_ROW + 16 * t;     // unit (i, t) of batch row g; + 8 nt rows, + 256 for the low plane
+    int aH[MT][4], aL[MT][4];
+    float bf[MT][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { aH[nt][j] = 0; aL[nt][j] = 0; bf[nt][j] = 0.f; }
+    static_for<0, 4>([&](auto i_) {
+        constexpr int I = decltype(i_)::value;
+        uint4 xh[MT], xl[MT];
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) {
+            xh[nt] = ld16(xb + nt * 8 * GQ_X8_ROW + 64 * I);
+            xl[nt] = ld16(xb + nt * 8 * GQ_X8_ROW + 64 * I + 256);
+        }
+        if constexpr (D::SCHEME == GQ_S16) {
+            static_for<0, 4>([&](auto r_) {
+                constexpr int RR = decltype(r_)::value, R = 4 * I + RR;
+                uint32_t a[2];
+                dec.template step16<R>(a);
+                int s0, s1;
+                dec.template iscale16<R>(s0, s1);
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt) {
+                    int th[4], tl[4];
+                    imma16<AS, true>(th, a, w4(xh[nt], RR));
+                    imma16<AS, false>(tl, a, w4(xl[nt], RR));
+                    aH[nt][0] += s0 * th[0]; aH[nt][1] += s0 * th[1]; aH[nt][2] += s1 * th[2]; aH[nt][3] += s1 * th[3];
+                    aL[nt][0] += s0 * tl[0]; aL[nt][1] += s0 * tl[1]; aL[nt][2] += s1 * tl[2]; aL[nt][3] += s1 * tl[3];
+                }
+            });
+        } else {
+            static_for<0, 2>([&](auto v_) {
+                constexpr int V = decltype(v_)::value, S = 2 * I + V;
+                uint32_t a[4];
+                dec.template step<S>(a);
+                int s0 = 1, s1 = 1;
+                float f0 = 1.f, f1 = 1.f;
+                if constexpr (D::SCHEME == GQ_S32) dec.template iscale<S>(s0, s1);
+                if constexpr (D::SCHEME == GQ_F32) dec.template fscale<S>(f0, f1);
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt) {
+                    const uint32_t bh0 = V ? xh[nt].z : xh[nt].x, bh1 = V ? xh[nt].w : xh[nt].y;
+                    const uint32_t bl0 = V ? xl[nt].z : xl[nt].x, bl1 = V ? xl[nt].w : xl[nt].y;
+                    if constexpr (D::SCHEME == GQ_FOLD) {
+                        imma32<AS, true>(aH[nt], a, bh0, bh1, aH[nt][0], aH[nt][1], aH[nt][2], aH[nt][3]);
+                        imma32<AS, false>(aL[nt], a, bl0, bl1, aL[nt][0], aL[nt][1], aL[nt][2], aL[nt][3]);
+                    } else {
+                        int th[4], tl[4];
+                        imma32<AS, true>(th, a, bh0, bh1, 0, 0, 0, 0);
+                        imma32<AS, false>(tl, a, bl0, bl1, 0, 0, 0, 0);
+                        if constexpr (D::SCHEME == GQ_S32) {
+                            aH[nt][0] += s0 * th[0]; aH[nt][1] += s0 * th[1]; aH[nt][2] += s1 * th[2]; aH[nt][3] += s1 * th[3];
+                            aL[nt][0] += s0 * tl[0]; aL[nt][1] += s0 * tl[1]; aL[nt][2] += s1 * tl[2]; aL[nt][3] += s1 * tl[3];
+                        } else {
+                            bf[nt][0] = fmaf(f0, (float)(th[0] * 256 + tl[0]), bf[nt][0]);
+                            bf[nt][1] = fmaf(f0, (float)(th[1] * 256 + tl[1]), bf[nt][1]);
+                            bf[nt][2] = fmaf(f1, (float)(th[2] * 256 + tl[2]), bf[nt][2]);
+                            bf[nt][3] = fmaf(f1, (float)(th[3] * 256 + tl[3]), bf[nt][3]);
+                        }
+                    }
+                }
+            });
+        }
+    });
+    float d0, d1;
+    dec.kscale(d0, d1);
+    uint32_t ac[4] = {0u, 0u, 0u, 0u};
+    float fc[2] = {0.f, 0.f};
+    if constexpr (D::NCORR > 0) {
+        dec.corr(ac, fc);
+        fc[0] *= -64.0f; fc[1] *= -64.0f;
+    }
+    const float z[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+        float tot[4];
+        if constexpr (D::SCHEME == GQ_F32) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tot[j] = bf[nt][j];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tot[j] = (j < 2 ? d0 : d1) * fmaf((float)aH[nt][j], 256.0f, (float)aL[nt][j]);
+        }
+        if constexpr (D::NCORR > 0) {
+            const uint8_t *sb = xs + (nt * 8 + g) * GQ_X8_ROW + GQ_X8_SUMS + 8 * t;
+            const uint2 bh = *reinterpret_cast<const uint2 *>(sb);
+            const uint2 bl = *reinterpret_cast<const uint2 *>(sb + 32);
+            float mm[4];
+            mma16816_z(mm, ac, bh.x, bh.y, z);
+            mma16816(mm, ac, bl.x, bl.y);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tot[j] = fmaf(fc[j >> 1], mm[j], tot[j]);
+        }
+        const float2 sx = *reinterpret_cast<const float2 *>(xs + xs_off + (nt * 8 + 2 * t) * 4);
+        acc[nt][0] = fmaf(sx.x, tot[0], acc[nt][0]);
+        acc[nt][1] = fmaf(sx.y, tot[1], acc[nt][1]);
+        acc[nt][2] = fmaf(sx.x, tot[2], acc[nt][2]);
+        acc[nt][3] = fmaf(sx.y, tot[3], acc[nt][3]);
+    }
+}
+
+
+template <int TYPE, int MT>
+__device__ __forceinline__ bool consume8(const Ring &r, int xs_off, int slab_off, const DecAux8 &aux, int lane, float (&acc)[MT][4]) {
+    for (int i = 0, s = 0, round = 0; i < r.nk; ++i) {
+#ifdef GQ_TRACE
+        const long long ta = clock64();
+#endif
+        if (!mbar_wait(r.full + s, round & 1)) return false;
+#ifdef GQ_TRACE
+        const long long tb = clock64();
+        if (i == 0 && lane == 0 && slab_off == 0) GQ_MARK(3);
+#endif
+        const uint8_t *st = r.smem + (size_t)s * r.stage_bytes;
+        slab_kblock8<TYPE, MT>(st + slab_off, st + r.wmax, xs_off, aux, lane, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(r.empty + s);
+#ifdef GQ_TRACE
+        if (lane == 0 && slab_off == 0 && blockIdx.x < 1024 && i < 64) {
+            long long *t = g_trace + ((size_t)blockIdx.x * 64 + i) * 4;
+            t[0] = ta; t[1] = tb; t[2] = clock64();
+        }
+#endif
+        if (++s == r.stages) { s = 0; ++round; }
     }
     return true;
 }
@@ -546,31 +837,49 @@ __device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const ui
 // kernels costs more in instruction-cache misses at every launch than the better fit gains.)  The 17..32-row form
 // is about 10 % faster with room for two CTAs (168 registers) than with the compiler's own 144; the 16- and 64-row
 // forms were best left alone.
-template <int MT, int MINB>
+//
+// FORM 0: fp16 form (activations as fp16, weights decoded to fp16 pairs, m16n8k16 f16 MMAs), used for 17..64 batch rows.
+// FORM 1: integer form (activations as two byte planes, weights decoded to 8-bit quads, m16n8k32 / m16n8k16 integer
+// MMAs), used for 1..16 batch rows: about half the instructions per weight.
+// ONLY: 0 compiles the decoders of all eleven types (the branch is per CTA); a GGML type id compiles that type alone,
+// for launches whose shards all share it (a smaller kernel; most launches of a real model are such).
+template <int MT, int FORM>
+__host__ __device__ constexpr int gq_stage_xbytes() { return FORM ? 8 * MT * GQ_X8_ROW + 32 * MT : 8 * MT * GQ_XROW_BYTES; }
+template <int FORM>
+__host__ __device__ constexpr int gq_iq3s_smem() { return FORM ? GQ_IQ3S8_SMEM_BYTES : GQ_IQ3S_SMEM_BYTES; }
+
+template <int MT, int MINB, int FORM, int ONLY>
 __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_grouped_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: [stages x (weights wbytes_max | activation tile)] [full barriers] [empty barriers] [IQ3_S grid]
+    // layout: [stages x (weights wbytes_max | activation tile)] [full barriers] [empty barriers] [IQ3_S grid] [reduction scratch]
     const int stages = p.stages, wmax = p.wbytes_max, M = p.M;
-    const int xbytes = 8 * MT * GQ_XROW_BYTES;
+    constexpr int xbytes = gq_stage_xbytes<MT, FORM>();
     const int stage_bytes = wmax + xbytes;
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)stages * stage_bytes);
     uint64_t *empty = full + stages;
     uint2 *grid_s = reinterpret_cast<uint2 *>(empty + stages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) GQ_MARK(0);
     const int32_t *d = p.desc + (int64_t)blockIdx.x * GQ_DESC_WORDS;
     const int64_t off = (int64_t)d[0] * 16;
-    const int type = d[1], col0 = d[2], nvalid = d[3], kb0 = d[4], kb1 = d[5], split_idx = d[6];
+    const int type = ONLY ? ONLY : d[1];
+    const int col0 = d[2], nvalid = d[3], kb0 = d[4], kb1 = d[5], split_idx = d[6];
     const int B = gq_type_bytes(type);
     const int tile_bytes = 64 * B;
     const int nk = kb1 - kb0;
+
+    Ring ring;
+    ring.smem = smem; ring.full = full; ring.empty = empty;
+    ring.stages = stages; ring.stage_bytes = stage_bytes; ring.wmax = wmax; ring.nk = nk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, GQ_CONSUMER_WARPS); }
         fence_barrier_init();
     }
-    if (p.has_iq3s && type == GQ_IQ3_S) {
-        for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]);
+    if ((ONLY == 0 || ONLY == GQ_IQ3_S) && p.has_iq3s && type == GQ_IQ3_S) {
+        if constexpr (FORM) { for (int i = threadIdx.x; i < 512; i += blockDim.x) reinterpret_cast<uint32_t *>(grid_s)[i] = iq3s_grid_entry8(c_iq3s_grid[i]); }
+        else { for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]); }
     }
     __syncthreads();
     // push-form split-K: a CTA may store into the split-0 CTA's shared memory only once that CTA is known to run;
@@ -578,6 +887,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     // closing barrier), long after everyone has arrived
     const bool push = p.cluster && p.cluster_push;
     if (push) cluster_arrive_relaxed();
+    if (threadIdx.x == 0) GQ_MARK(1);
 
     if (warp == GQ_CONSUMER_WARPS) {
         // ---- producer: one thread; per k-block one bulk copy of the weight tile and one of the activation tile.
@@ -586,7 +896,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         // kernel behind this one is allowed to start launching when this CTA has two k-blocks left. ----
         if (lane == 0) {
             const uint8_t *src = p.packed + off + (int64_t)kb0 * tile_bytes;
-            const uint32_t abytes = (uint32_t)M * GQ_XROW_BYTES;
+            const uint32_t abytes = FORM ? (uint32_t)gq_x8_tile_bytes(M) : (uint32_t)M * GQ_XROW_BYTES;
             const uint8_t *xsrc = p.xt + (int64_t)kb0 * abytes;
             const int pre = nk < stages ? nk : stages;
             for (int i = 0; i < pre; ++i) {
@@ -594,14 +904,18 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
                 bulk_g2s(smem + (size_t)i * stage_bytes, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + i);
             }
             pdl_wait();
+            GQ_MARK(2);
             for (int i = 0; i < pre; ++i) bulk_g2s(smem + (size_t)i * stage_bytes + wmax, xsrc + (int64_t)i * abytes, abytes, full + i);
             if (nk - pre <= 2) pdl_trigger();
             for (int i = pre, s = 0, round = 1; i < nk; ++i) {
-                if (!mbar_wait(empty + s, (round - 1) & 1)) { atomicExch(p.status, GQ_DEV_TIMEOUT); break; }
+                if (!mbar_wait_parked(empty + s, (round - 1) & 1)) { atomicExch(p.status, GQ_DEV_TIMEOUT); break; }
                 uint8_t *st = smem + (size_t)s * stage_bytes;
                 mbar_expect_tx(full + s, (uint32_t)tile_bytes + abytes);
                 bulk_g2s(st, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + s);
                 bulk_g2s(st + wmax, xsrc + (int64_t)i * abytes, abytes, full + s);
+#ifdef GQ_TRACE
+                if (blockIdx.x < 1024 && i < 64) g_trace[((size_t)blockIdx.x * 64 + i) * 4 + 3] = clock64();
+#endif
                 if (i == nk - 3) pdl_trigger();
                 if (++s == stages) { s = 0; ++round; }
             }
@@ -624,36 +938,57 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     }
 
     // ---- consumers ----
-    DecAux aux;
-    aux.iq3s_grid = grid_s;
-    {
-        uint32_t tb[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            tb[j] = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) tb[j] |= (uint32_t)(uint8_t)(c_iq4_kvalues[4 * j + i] + 128) << (8 * i);
-        }
-        aux.iq4 = {tb[0], tb[1], tb[2], tb[3]};
-    }
     float acc[MT][4];
 #pragma unroll
     for (int nt = 0; nt < MT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
     bool ok = true;
     const int slab_off = warp * 16 * B;
-#define GQ_CONSUME(T) case T: ok = consume<T, MT>(smem, full, empty, stages, stage_bytes, wmax, slab_off, nk, aux, lane, acc); break;
-    switch (type) {
-        GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
-        GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS)
+    // the IQ4 codebook in four registers: signed bytes for the integer form, + 128 for the fp16 form
+    Iq4Table iq4;
+    {
+        uint32_t tb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            tb[j] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tb[j] |= (uint32_t)(uint8_t)(c_iq4_kvalues[4 * j + i] + (FORM ? 0 : 128)) << (8 * i);
+        }
+        iq4 = {tb[0], tb[1], tb[2], tb[3]};
     }
+    if constexpr (FORM) {
+        DecAux8 aux;
+        aux.iq3s_grid = reinterpret_cast<const uint32_t *>(grid_s);
+        aux.iq4 = iq4;
+        const int xs_off = M * GQ_X8_ROW;
+#define GQ_CONSUME(T) case T: ok = consume8<T, MT>(ring, xs_off, slab_off, aux, lane, acc); break;
+        if constexpr (ONLY != 0) {
+            ok = consume8<(ONLY ? ONLY : GQ_Q4_K), MT>(ring, xs_off, slab_off, aux, lane, acc);
+        } else {
+            switch (type) {
+                GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
+                GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS)
+            }
+        }
 #undef GQ_CONSUME
+    } else {
+        DecAux aux;
+        aux.iq3s_grid = grid_s;
+        aux.iq4 = iq4;
+#define GQ_CONSUME(T) case T: ok = consume<T, MT>(ring, slab_off, aux, lane, acc); break;
+        switch (type) {
+            GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
+            GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS)
+        }
+#undef GQ_CONSUME
+    }
     if (!ok && lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT);   // the result is then incomplete; the status word says so
+    if (threadIdx.x == 0) GQ_MARK(4);
 
     // ---- epilogue: rows of the MMA are output columns, columns of the MMA are batch rows ----
     const int g = lane >> 2, t = lane & 3;
     // scratch of its own behind the ring (a slower warp may still read the ring): GQ_CONSUMER_WARPS x MT x 512 bytes
-    float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0));
+    float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? gq_iq3s_smem<FORM>() : 0));
     if (push) {
         cluster_wait();         // the rendezvous entered at the start: every CTA of the cluster is running
         // split-K inside a cluster, push form: the CTAs of splits 1.. store their accumulators into their slot of the
@@ -707,7 +1042,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             for (int j = 0; j < 4; ++j) {
                 const int rl = g + 8 * (j >> 1), n = nt * 8 + 2 * t + (j & 1);
                 const bool valid = ok && warp * 16 + rl < nvalid && n < p.M;
-                blk[n * 16 + rl] = __float2bfloat16_rn(valid ? acc[nt][j] * p.ex[n] : 0.0f);
+                blk[n * 16 + rl] = __float2bfloat16_rn(valid ? (FORM ? acc[nt][j] : acc[nt][j] * p.ex[n]) : 0.0f);
             }
         __syncwarp();
         const int ncols = nvalid - warp * 16 < 16 ? nvalid - warp * 16 : 16;
@@ -725,11 +1060,12 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             const int r = warp * 16 + g + 8 * (j >> 1);      // row inside the 64-row tile
             const int n = nt * 8 + 2 * t + (j & 1);          // batch row
             if (ok && r < nvalid && n < p.M) {
-                const float v = acc[nt][j] * p.ex[n];
+                const float v = FORM ? acc[nt][j] : acc[nt][j] * p.ex[n];    // the integer form scales per k-block
                 if (p.split == 1 || p.cluster) p.y[(int64_t)n * p.ldy + col0 + r] = __float2bfloat16_rn(v);
                 else p.partials[((int64_t)split_idx * p.M + n) * p.n_total + col0 + r] = v;
             }
         }
+    if (threadIdx.x == 0) GQ_MARK(5);
 }
 
 // Y = sum over splits of the fp32 partials, rounded once to bf16 (reference: sum_partials,
@@ -747,13 +1083,6 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const float *__restri
 // ---------------------------------------------------------------------------------------------------
 // C ABI
 // ---------------------------------------------------------------------------------------------------
-// programmatic dependent launch can be switched off for A/B timing (GQ_NO_PDL=1); the kernels are correct either way
-static int use_pdl() {
-    static int v = -1;
-    if (v < 0) { const char *e = getenv("GQ_NO_PDL"); v = (e && e[0] == '1') ? 0 : 1; }
-    return v;
-}
-
 static int ensure_tables() {
     // per-device one-time upload of the two format tables into constant memory
     static std::atomic<unsigned long long> done_mask{0};
@@ -877,22 +1206,21 @@ extern "C" int64_t gq_workspace_bytes(int64_t M, int64_t K, int64_t n_total, int
     return ws_layout(M, K, n_total, split, nullptr, nullptr);
 }
 
-template <int MT, int MINB>
+template <int MT, int MINB, int FORM, int ONLY>
 static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream) {
-    const int xbytes = 8 * MT * GQ_XROW_BYTES;
+    constexpr int xbytes = gq_stage_xbytes<MT, FORM>();
     const int stage_bytes = p.wbytes_max + xbytes;
-    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) +
+    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? gq_iq3s_smem<FORM>() : 0) +
                         (size_t)GQ_CONSUMER_WARPS * MT * 512 * (p.cluster_push ? p.split - 1 : 1);
-    // opt in once per device to the largest dynamic shared memory any launch of this variant can ask for
+    if (smem > 232448) return GQ_ERR_LIMIT;
+    // opt in once per device to the largest dynamic shared memory a CTA can have
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
-        const int max_smem = 8 * (64 * 272 + xbytes) + 8 * 16 + GQ_IQ3S_SMEM_BYTES + GQ_CONSUMER_WARPS * MT * 512;
-        GQ_CUDA(cudaFuncSetAttribute(gemv_grouped_kernel<MT, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem > 232448 ? 232448 : max_smem));
+        GQ_CUDA(cudaFuncSetAttribute(gemv_grouped_kernel<MT, MINB, FORM, ONLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
         if (dev < 64) done_mask.fetch_or(1ull << dev);
     }
-    if (smem > 232448) return GQ_ERR_LIMIT;
     {
         cudaLaunchConfig_t cfg = {};
         cudaLaunchAttribute attr[2];
@@ -902,29 +1230,39 @@ static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream)
             attr[na].val.clusterDim.x = (unsigned)p.split; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1;
             ++na;
         }
-        if (use_pdl()) {
-            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[na].val.programmaticStreamSerializationAllowed = 1;
-            ++na;
-        }
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
         cfg.gridDim = dim3((unsigned)n_desc); cfg.blockDim = dim3(32 * (GQ_CONSUMER_WARPS + 1)); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
         cfg.attrs = attr; cfg.numAttrs = na;
-        GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_grouped_kernel<MT, MINB>, p));
+        GQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_grouped_kernel<MT, MINB, FORM, ONLY>, p));
     }
     GQ_LAUNCHED();
     return GQ_OK;
 }
 
+// integer form, M <= 8: one instantiation per type for runs of a single type, the all-types one otherwise
+static int launch_gemv8_m8(const GemvParams &p, int64_t n_desc, cudaStream_t st, int only) {
+    switch (only) {
+#define GQ_ONE(T) case T: return launch_gemv<1, 4, 1, T>(p, n_desc, st);
+        GQ_ONE(GQ_Q4_0) GQ_ONE(GQ_Q5_0) GQ_ONE(GQ_Q8_0) GQ_ONE(GQ_Q2_K) GQ_ONE(GQ_Q3_K) GQ_ONE(GQ_Q4_K)
+        GQ_ONE(GQ_Q5_K) GQ_ONE(GQ_Q6_K) GQ_ONE(GQ_IQ4_NL) GQ_ONE(GQ_IQ3_S) GQ_ONE(GQ_IQ4_XS)
+#undef GQ_ONE
+        default: return launch_gemv<1, 4, 1, 0>(p, n_desc, st);
+    }
+}
+
 extern "C" int gq_run_info(int n_shards, const int32_t *types) {
     if (n_shards <= 0 || !types) return GQ_ERR_ARG;
-    int maxb = 0, iq3s = 0;
+    int maxb = 0, iq3s = 0, single = types[0];
     for (int i = 0; i < n_shards; ++i) {
         const int B = gq_type_bytes(types[i]);
         if (!B) return GQ_ERR_TYPE;
         if (B > maxb) maxb = B;
         if (types[i] == GQ_IQ3_S) iq3s = 1;
+        if (types[i] != single) single = 0;
     }
-    return maxb | (iq3s << 16);
+    return maxb | (iq3s << 16) | (single << 17);
 }
 
 static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
@@ -942,14 +1280,20 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     if (int rc = ensure_tables()) return rc;
     cudaStream_t st = (cudaStream_t)stream;
 
+    const int form = M <= GQ_GEMV8_MAX_ROWS ? 1 : 0;
     if (phases & 1) {
         cudaLaunchConfig_t cfg = {};
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.gridDim = dim3((unsigned)M); cfg.blockDim = dim3(GQ_PREP_THREADS); cfg.dynamicSmemBytes = 0; cfg.stream = st;
-        cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
-        GQ_CUDA(cudaLaunchKernelEx(&cfg, prep_x_kernel, (const __nv_bfloat16 *)x_dev, ldx, (int)K, (int)M, ws.ex, ws.xt, ws.status));
+        cfg.dynamicSmemBytes = 0; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
+        if (form) {
+            cfg.gridDim = dim3((unsigned)(K / GQ_QK), (unsigned)((M + GQ_PREP8_WARPS - 1) / GQ_PREP8_WARPS)); cfg.blockDim = dim3(32 * GQ_PREP8_WARPS);
+            GQ_CUDA(cudaLaunchKernelEx(&cfg, prep_x8_kernel, (const __nv_bfloat16 *)x_dev, ldx, (int)M, ws.xt, ws.status));
+        } else {
+            cfg.gridDim = dim3((unsigned)M); cfg.blockDim = dim3(GQ_PREP_THREADS);
+            GQ_CUDA(cudaLaunchKernelEx(&cfg, prep_x_kernel, (const __nv_bfloat16 *)x_dev, ldx, (int)K, (int)M, ws.ex, ws.xt, ws.status));
+        }
         GQ_LAUNCHED();
     }
     if (!(phases & 6)) return GQ_OK;
@@ -965,11 +1309,6 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     // split-K up to 8 reduces inside a thread-block cluster (portable cluster size); larger splits keep the fp32
     // partials and the separate sum
     p.cluster = (split > 1 && split <= 8 && n_desc % split == 0) ? 1 : 0;
-    {
-        static int no_cluster = -1;   // tuning knob: GQ_NO_CLUSTER=1 sends every split through the fp32 partials instead
-        if (no_cluster < 0) { const char *e = getenv("GQ_NO_CLUSTER"); no_cluster = (e && e[0] == '1') ? 1 : 0; }
-        if (no_cluster) p.cluster = 0;
-    }
     p.cluster_push = 0;
     p.pf_ptr = (next_packed_dev && next_bytes > 0 && !((uintptr_t)next_packed_dev & 15)) ? (const uint8_t *)next_packed_dev : nullptr;
     p.pf_bytes = next_bytes;
@@ -984,12 +1323,12 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     {
         // ring depth: four stages when four CTAs of them still fit an SM's shared memory, else three (swept on the
         // 64-layer stack: deeper rings with fewer resident CTAs were slower overall)
-        const int stage_bytes = p.wbytes_max + 8 * mt * GQ_XROW_BYTES;
+        const int xb = mt == 1 ? gq_stage_xbytes<1, 1>() : mt == 2 ? gq_stage_xbytes<2, 1>() : 8 * mt * GQ_XROW_BYTES;
+        const int stage_bytes = p.wbytes_max + xb;
         // (an SM has 228 KB of shared memory and the system keeps 1 KB of it per resident CTA)
-        const int fixed = 64 + (p.has_iq3s ? GQ_IQ3S_SMEM_BYTES : 0) + 1024, red1 = GQ_CONSUMER_WARPS * mt * 512;
+        const int fixed = 64 + (p.has_iq3s ? (form ? GQ_IQ3S8_SMEM_BYTES : GQ_IQ3S_SMEM_BYTES) : 0) + 1024, red1 = GQ_CONSUMER_WARPS * mt * 512;
         // split-K in a cluster: the push form of the reduction needs a scratch slot per other split in every CTA; it
         // is used when that costs no resident CTA (the ring then has three stages; its depth does not matter)
-        p.cluster_push = 0;
         if (p.cluster) {
             const int pull = (228 * 1024) / (3 * stage_bytes + fixed + red1), push = (228 * 1024) / (3 * stage_bytes + fixed + red1 * (split - 1));
             const int cap = mt == 1 ? 4 : 8;     // resident CTAs the register budget allows anyway
@@ -997,17 +1336,14 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         }
         const int red = p.cluster_push ? red1 * (split - 1) : red1;
         p.stages = (4 * (4 * stage_bytes + fixed + red) <= 228 * 1024) ? 4 : 3;
-        static int forced = -1;   // tuning knob: GQ_STAGES=n overrides the ring depth
-        if (forced < 0) { const char *e = getenv("GQ_STAGES"); forced = e ? atoi(e) : 0; }
-        if (forced >= 2 && forced <= 8) p.stages = forced;
     }
     int rc = GQ_OK;
     if (phases & 2) {
         switch (mt) {
-            case 1: rc = launch_gemv<1, 4>(p, n_desc, st); break;
-            case 2: rc = launch_gemv<2, 0>(p, n_desc, st); break;
-            case 4: rc = launch_gemv<4, 2>(p, n_desc, st); break;
-            default: rc = launch_gemv<8, 0>(p, n_desc, st); break;
+            case 1: rc = launch_gemv8_m8(p, n_desc, st, (run_info >> 17) & 31); break;
+            case 2: rc = launch_gemv<2, 3, 1, 0>(p, n_desc, st); break;
+            case 4: rc = launch_gemv<4, 2, 0, 0>(p, n_desc, st); break;
+            default: rc = launch_gemv<8, 0, 0, 0>(p, n_desc, st); break;
         }
     }
     if (rc) return rc;

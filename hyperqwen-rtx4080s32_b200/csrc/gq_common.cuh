@@ -68,6 +68,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     return false;
 }
 
+// The same for a thread that expects to wait long and has nothing else to do (the producer of a stage ring waiting
+// for a free stage): each poll carries a suspend-time hint, so the hardware parks the thread until the phase completes
+// or the hint runs out, and a failed poll is followed by a short sleep — a waiting producer then costs a handful of
+// issue slots per k-block instead of one poll every few cycles.
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    uint64_t t0 = 0;
+    for (uint32_t i = 0; i < GQ_SPIN_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity), "r"(20000u)
+            : "memory");
+        if (ok) return true;
+        __nanosleep(64);
+        if ((i & 63u) == 63u) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > GQ_WAIT_LIMIT_NS) return false;
+        }
+    }
+    return false;
+}
+
 // ---- bulk copy global -> shared, completion counted on an mbarrier (bytes a multiple of 16, both
 // addresses 16-byte aligned) -------------------------------------------------------------------
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {

@@ -309,9 +309,9 @@ struct Dec<GQ_Q8_0> {
         for (int u = 0; u < 2; ++u)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint32_t x = w4(q[P], 2 * h + u) ^ 0x80808080u;    // int8 + 128
-                a[u][h] = prmt(x, GQ_MAGICB, 0x5150u);
-                a[u][2 + h] = prmt(x, GQ_MAGICB, 0x5352u);
+                const uint32_t x = w4(q[P], 2 * h + u) ^ 0x80808080u;    // int8 + 128, bytes hold weights (0,2,1,3)
+                a[u][h] = prmt(x, GQ_MAGICB, 0x5250u);
+                a[u][2 + h] = prmt(x, GQ_MAGICB, 0x5351u);
             }
     }
     template <int G>

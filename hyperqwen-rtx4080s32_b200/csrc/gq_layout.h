@@ -69,9 +69,10 @@ GQ_HD inline int gq_slab_src(int type, int p, int *row, int *byte) {
     const int B = gq_type_bytes(type);
     const int C = gq_type_chunks(type);
     if (B == 0 || p < 0 || p >= 16 * B) return -1;
-    // the byte order inside a 4-byte word of a lane's chunk: mask-extracted types put weights (0,2,1,3) so
-    // that bytes 0 and 2 (the low bytes of the two 16-bit halves) are k-neighbours; prmt-extracted types keep
-    // the natural order
+    // the byte order inside a 4-byte word of a lane's chunk: types whose stored bytes are read in place (masks,
+    // or the int8 weights of Q8_0) put weights (0,2,1,3), so that bytes 0 and 2 (the low bytes of the two 16-bit
+    // halves) are k-neighbours and an 8-bit quad has the order the activation planes use; types that go through a
+    // byte lookup keep the natural order (the lookup emits whatever order it likes)
     if (p < 512 * C) {
         const int c = p >> 9, l = (p >> 4) & 31, e = (p >> 2) & 3, z = p & 3;
         const int g = l >> 2, t = l & 3;
@@ -91,7 +92,7 @@ GQ_HD inline int gq_slab_src(int type, int p, int *row, int *byte) {
                 return 0;
             case GQ_Q8_0: {
                 const int r = 2 * c + u;          // run 0..15
-                *row = g + 8 * h; *byte = 34 * (r >> 1) + 2 + 16 * (r & 1) + 4 * t + z; return 0;
+                *row = g + 8 * h; *byte = 34 * (r >> 1) + 2 + 16 * (r & 1) + 4 * t + im; return 0;
             }
             case GQ_Q4_0: { const int b = 2 * c + u; *row = g + 8 * h; *byte = 18 * b + 2 + 4 * t + im; return 0; }
             case GQ_IQ4_NL: { const int b = 2 * c + u; *row = g + 8 * h; *byte = 18 * b + 2 + 4 * t + z; return 0; }

@@ -331,11 +331,12 @@ def test_wide_run_dispatch_takes_the_tcgen05_path_from_41_rows():
         assert oracle.rel_err(y.float().cpu().numpy(), ref_gemm(x, raw, t)) < TOL_TIGHT
         same = torch.equal(y, ops.prefill_gemm(x, packed, d1, n_out))
         assert same == (m > 40)
-        if 32 < m <= 40:      # two launches of the grouped kernel: rows are independent of their batch
+        if 32 < m <= 40:      # two launches of the grouped kernel: 32 rows in the fp16 form, the rest in the integer form
             s = ops.grouped_split_for(n_out // 64, nb, m=m, block_bytes=bb, sms=ops.sm_count(dev()))
             s = s if s in splits else 1
             whole = ops.grouped_gemm(x, packed, descs[splits.index(s)], s, [t], n_out)
-            assert torch.equal(y, whole)
+            assert torch.equal(y[:32], whole[:32])       # rows of the fp16 form do not depend on their batch
+            assert oracle.rel_err(y[32:].float().cpu().numpy(), whole[32:].float().cpu().numpy()) < TOL_TIGHT
 
 
 def test_prefill_full_size_down_projection_properties():
