@@ -46,6 +46,8 @@ SIGNATURES = {
     "gq_prefill_workspace_bytes": (_i64, [_i64, _i64]),
     "gq_gemm_prefill": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _vp]),
     "gq_read_status": (_i32, [_vp, _i64, _vp]),
+    "gq_device_status": (_i32, [_i32, _vp]),
+    "gq_set_peer_wait_limit_ns": (_i32, [_i64]),
     "gq_last_cuda_error": (ctypes.c_char_p, []),
     "gq_launch_count": (_i64, []),
 }

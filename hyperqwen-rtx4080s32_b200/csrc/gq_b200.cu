@@ -5,6 +5,8 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <atomic>
+#include <mutex>
+#include <unordered_map>
 #include "../../include/gq_b200.h"
 #include "gq_decode.cuh"
 #include "gq_decode8.cuh"
@@ -120,6 +122,17 @@ __global__ void __launch_bounds__(256) unrepack_kernel(int type, int B, const ui
 // ---------------------------------------------------------------------------------------------------
 __constant__ uint32_t c_iq3s_grid[512];
 __constant__ int8_t c_iq4_kvalues[16];
+
+// A bounded wait that runs out is reported twice: in the status word of the launch's workspace (gq_read_status) and in
+// this per-device word, which keeps the largest code seen since it was last read (gq_device_status) — a caller that
+// drops its workspace after every call, or has none to read (the no-allocation entry point), still learns of it.
+__device__ int g_sticky_status;
+__device__ __forceinline__ void report_status(int *status, int code) {
+    atomicExch(status, code);
+    atomicMax(&g_sticky_status, code);
+}
+// time limit of the waits on data from another GPU (the fused and the separate all-reduce), nanoseconds
+static std::atomic<unsigned long long> g_peer_wait_ns{GQ_WAIT_LIMIT_NS};
 
 #include "gq_prefill.cuh"
 
@@ -350,6 +363,10 @@ __global__ void __launch_bounds__(GQ_PREP_THREADS) prep_x_kernel(const __nv_bflo
 }
 
 
+#ifdef GQ_TRACE
+__device__ unsigned long long g_ptl[64 * 4];
+extern "C" int gq_prep_timeline_read(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, g_ptl, sizeof g_ptl); }
+#endif
 // ---------------------------------------------------------------------------------------------------
 // activation preparation, integer form (1..16 batch rows): one warp per (batch row, k-block).  The 256 activations
 // become 16-bit fixed point at a power-of-two scale of their own (exact for every value within 2^-7 of the block's
@@ -363,8 +380,14 @@ __global__ void __launch_bounds__(32 * GQ_PREP8_WARPS) prep_x8_kernel(const __nv
                                                                       int *status) {
     const int lane = threadIdx.x & 31, kb = blockIdx.x;
     const int m = blockIdx.y * GQ_PREP8_WARPS + (threadIdx.x >> 5);
+#ifdef GQ_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 64) g_ptl[blockIdx.x * 4 + 0] = global_timer_ns();
+#endif
     pdl_trigger();    // the grouped kernel behind this one may start fetching weights
     pdl_wait();       // whatever ran before (possibly still reading this workspace) has finished
+#ifdef GQ_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 64) g_ptl[blockIdx.x * 4 + 1] = global_timer_ns();
+#endif
     if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *status = 0;
     if (m >= M) return;
     const __nv_bfloat16 *xr = x + (int64_t)m * ldx + (int64_t)kb * GQ_QK + 8 * lane;
@@ -419,6 +442,9 @@ __global__ void __launch_bounds__(32 * GQ_PREP8_WARPS) prep_x8_kernel(const __nv
         so[16 + r] = lo;
     }
     if (lane == 0) *reinterpret_cast<float *>(xt + (int64_t)kb * gq_x8_tile_bytes(M) + (int64_t)M * GQ_X8_ROW + 4 * m) = inv;
+#ifdef GQ_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 64) g_ptl[blockIdx.x * 4 + 2] = global_timer_ns();
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -437,6 +463,7 @@ __global__ void __launch_bounds__(32 * GQ_PREP8_WARPS) prep_x8_kernel(const __nv
 // tile, consumer warp): 16 output columns of all batch rows — the grain at which ranks exchange and sum.
 struct ArFused {
     int world, rank, units;          // world == 0: plain output, no exchange
+    unsigned long long wait_ns;      // time limit of the wait for the peers' words
     int64_t slot_bytes;
     uint8_t *buf[GQ_AR_MAX_WORLD];
     uint32_t *counters;
@@ -810,7 +837,7 @@ __device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const ui
                 if ((it & 255u) == 255u) {      // the clock is read only once a wait has become long
                     const uint64_t now = global_timer_ns();
                     if (t0 == 0) t0 = now;
-                    if (now - t0 > GQ_WAIT_LIMIT_NS) { fail = true; break; }
+                    if (now - t0 > a.wait_ns) { fail = true; break; }
                 }
             }
             if (fail) break;
@@ -825,7 +852,7 @@ __device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const ui
     }
     fail = __any_sync(0xffffffffu, fail);
     if (lane == 0) {
-        if (fail) atomicExch(p.status, GQ_DEV_TIMEOUT);
+        if (fail) report_status(p.status, GQ_DEV_TIMEOUT);
         a.counters[unit] = seq;
     }
 }
@@ -908,7 +935,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             for (int i = 0; i < pre; ++i) bulk_g2s(smem + (size_t)i * stage_bytes + wmax, xsrc + (int64_t)i * abytes, abytes, full + i);
             if (nk - pre <= 2) pdl_trigger();
             for (int i = pre, s = 0, round = 1; i < nk; ++i) {
-                if (!mbar_wait_parked(empty + s, (round - 1) & 1)) { atomicExch(p.status, GQ_DEV_TIMEOUT); break; }
+                if (!mbar_wait_parked(empty + s, (round - 1) & 1)) { report_status(p.status, GQ_DEV_TIMEOUT); break; }
                 uint8_t *st = smem + (size_t)s * stage_bytes;
                 mbar_expect_tx(full + s, (uint32_t)tile_bytes + abytes);
                 bulk_g2s(st, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + s);
@@ -982,7 +1009,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         }
 #undef GQ_CONSUME
     }
-    if (!ok && lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT);   // the result is then incomplete; the status word says so
+    if (!ok && lane == 0) report_status(p.status, GQ_DEV_TIMEOUT);   // the result is then incomplete; the status word says so
     if (threadIdx.x == 0) GQ_MARK(4);
 
     // ---- epilogue: rows of the MMA are output columns, columns of the MMA are batch rows ----
@@ -1047,7 +1074,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         __syncwarp();
         const int ncols = nvalid - warp * 16 < 16 ? nvalid - warp * 16 : 16;
         if (ncols > 0) {
-            if (((col0 | ncols | (int)p.n_total) & 1) && lane == 0) atomicExch(p.status, GQ_DEV_BAD_SHAPE);    // pairs of columns travel together
+            if (((col0 | ncols | (int)p.n_total) & 1) && lane == 0) report_status(p.status, GQ_DEV_BAD_SHAPE);    // pairs of columns travel together
             else fused_allreduce_block(p, reinterpret_cast<const uint32_t *>(blk), (int)(blockIdx.x / (unsigned)p.split) * GQ_CONSUMER_WARPS + warp,
                                        col0 + warp * 16, ncols, lane);
         }
@@ -1430,7 +1457,22 @@ extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K
     if (max_m < 1 || max_m > GQ_MAX_GEMV_ROWS || M > max_m || n_total > max_n_total) return GQ_ERR_SHAPE;
     ArFused ar = {};
     ar.world = world; ar.rank = rank; ar.units = (int)fused_ar_units(max_n_total);
+    ar.wait_ns = g_peer_wait_ns.load();
     if (n_total & 1) return GQ_ERR_SHAPE;
+    if (world > 1 && M > 0 && n_total > 0 && n_desc > 0) {
+        // a buffer serves one output width: the words' positions depend on n_total while the call numbers are kept per
+        // (tile, warp), so a second width on the same buffer could meet a stale word that carries a current number
+        static std::mutex mu;
+        static std::unordered_map<uint64_t, int64_t> bound;
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = bound.find(peer_buffers[rank]);
+        if (it == bound.end()) bound.emplace(peer_buffers[rank], n_total);
+        else if (it->second != n_total) {
+            snprintf(g_cuda_err, sizeof g_cuda_err, "gq_gemv_grouped_allreduce: this buffer exchanges outputs of %lld columns, the call has %lld",
+                     (long long)it->second, (long long)n_total);
+            return GQ_ERR_ARG;
+        }
+    }
     ar.slot_bytes = align256(max_m * max_n_total * 4);
     const int64_t header = fused_ar_header(max_n_total);
     for (int p = 0; p < world; ++p) {
@@ -1451,7 +1493,6 @@ extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K
 // number lives in device memory (one counter per CTA) so a captured CUDA graph replays correctly.
 // The reference has no collective of its own on this path (docs/multi-gpu.md:8-13 leaves it to vLLM's NCCL).
 #define GQ_AR_CTAS 16
-#define GQ_AR_SPIN_LIMIT (1u << 25)
 
 struct ArPeers {
     uint8_t *buf[GQ_AR_MAX_WORLD];      // data area of each rank's buffer: [2 sets][world][slot_bytes]
@@ -1459,7 +1500,8 @@ struct ArPeers {
 };
 
 __global__ void __launch_bounds__(256) allreduce_push_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, int64_t n_vec, int rank,
-                                                             int world, ArPeers peers, int64_t slot_bytes, uint32_t *counters, int *status) {
+                                                             int world, ArPeers peers, int64_t slot_bytes, uint32_t *counters, int *status,
+                                                             unsigned long long wait_ns) {
     __shared__ uint32_t s_seq;
     __shared__ int s_fail;
     const int c = blockIdx.x, G = gridDim.x;
@@ -1479,16 +1521,21 @@ __global__ void __launch_bounds__(256) allreduce_push_kernel(const uint4 *__rest
         uint32_t *f = peers.flags[threadIdx.x] + ((int64_t)set * world + rank) * G + c;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
         const uint32_t *mine = peers.flags[rank] + ((int64_t)set * world + threadIdx.x) * G + c;
-        uint32_t it = 0, v;
-        for (;;) {
+        uint32_t v;
+        uint64_t t0 = 0;
+        for (uint32_t it = 0;; ++it) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
             if (v == seq) break;
-            if (++it > GQ_AR_SPIN_LIMIT) { s_fail = 1; break; }
+            if ((it & 255u) == 255u) {      // the clock is read only once a wait has become long
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > wait_ns || it > GQ_SPIN_LIMIT) { s_fail = 1; break; }
+            }
         }
     }
     __syncthreads();
     if (s_fail) {
-        if (threadIdx.x == 0) { atomicExch(status, GQ_DEV_TIMEOUT); counters[c] = seq; }
+        if (threadIdx.x == 0) { report_status(status, GQ_DEV_TIMEOUT); counters[c] = seq; }
         return;
     }
     const uint8_t *base = peers.buf[rank] + (int64_t)set * world * slot_bytes;
@@ -1533,7 +1580,7 @@ extern "C" int gq_allreduce_push(const void *in_dev, void *out_dev, int64_t n_by
     uint32_t *counters = reinterpret_cast<uint32_t *>(own + 2 * GQ_AR_MAX_WORLD * GQ_AR_CTAS * 4);
     int *status = reinterpret_cast<int *>(own + 2 * GQ_AR_MAX_WORLD * GQ_AR_CTAS * 4 + GQ_AR_CTAS * 4);
     allreduce_push_kernel<<<GQ_AR_CTAS, 256, 0, (cudaStream_t)stream>>>((const uint4 *)in_dev, (uint4 *)out_dev, n_bytes / 16, rank, world, peers,
-                                                                     align256(max_bytes), counters, status);
+                                                                     align256(max_bytes), counters, status, g_peer_wait_ns.load());
     GQ_LAUNCHED();
     return GQ_OK;
 }
@@ -1597,6 +1644,24 @@ extern "C" int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t 
         case 128: return launch_prefill<128>(p, (const __nv_bfloat16 *)x_dev, ldx, ex, xp, st);
         default: return launch_prefill<256>(p, (const __nv_bfloat16 *)x_dev, ldx, ex, xp, st);
     }
+}
+
+extern "C" int gq_device_status(int clear, void *stream) {
+    int v = 0;
+    GQ_CUDA(cudaMemcpyFromSymbolAsync(&v, g_sticky_status, sizeof v, 0, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    GQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (clear && v != 0) {
+        const int zero = 0;
+        GQ_CUDA(cudaMemcpyToSymbolAsync(g_sticky_status, &zero, sizeof zero, 0, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+        GQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    }
+    return v;
+}
+
+extern "C" int gq_set_peer_wait_limit_ns(int64_t ns) {
+    if (ns < 1000 || ns > 60000000000ll) return GQ_ERR_ARG;
+    g_peer_wait_ns.store((unsigned long long)ns);
+    return GQ_OK;
 }
 
 extern "C" int gq_read_status(const void *workspace_dev, int64_t workspace_bytes, void *stream) {

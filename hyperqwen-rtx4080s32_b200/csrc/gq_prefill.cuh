@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, 1) gemm_prefill_kernel(const Pr
     }
     if (!ok) {
         // a bounded wait ran out: report it, and give copies and MMAs still in flight a bounded time to land
-        if (lane == 0) atomicExch(p.status, GQ_DEV_TIMEOUT);
+        if (lane == 0) report_status(p.status, GQ_DEV_TIMEOUT);
         for (int i = 0; i < 100; ++i) __nanosleep(10000);
     }
     tc_fence_before();

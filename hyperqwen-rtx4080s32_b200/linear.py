@@ -21,6 +21,8 @@ It does not import vLLM: `layer` is any torch.nn.Module.  Inside vLLM the class 
 """
 from __future__ import annotations
 
+import itertools
+
 from typing import Any
 
 import torch
@@ -167,65 +169,84 @@ class GGUFLinearMethod:
         weight.shard_offset_map = shard_offset_map
         data_container.clear()
 
-    def _create_tiles(self, layer: torch.nn.Module) -> None:
-        """Every shard (or the whole weight of a layer whose shards share one type) is repacked tile-major
-        once and the raw rows are freed (gguf-tiles-all-types.patch:73-131).  A layer flagged
-        `gguf_is_embedding` (the token embedding, whose rows are gathered, never multiplied) stays raw."""
+    @staticmethod
+    def _is_token_embedding(layer: torch.nn.Module) -> bool:
+        """The token embedding's rows are gathered, never multiplied through apply, so it is the one GGUF weight
+        that stays raw; the LM head, which vLLM derives from the same class, is multiplied and is tiled
+        (gguf-tiles-all-types.patch:80-89 tests isinstance(VocabParallelEmbedding) and not isinstance(ParallelLMHead);
+        the same test by class name here, so that the module imports without vLLM)."""
         if getattr(layer, "gguf_is_embedding", False):
-            return
-        tiles, rows, types = {}, {}, {}
+            return True
+        names = {c.__name__ for c in type(layer).__mro__}
+        return "VocabParallelEmbedding" in names and "ParallelLMHead" not in names
+
+    @staticmethod
+    def _weight_tensors(layer: torch.nn.Module):
+        """The layer's raw weight tensors in output order as (key, rows, type, drop): one entry per shard of a
+        mixed-type merged layer (key = shard id), otherwise a single entry "__all__" for the whole weight when it has
+        one type.  drop() replaces the raw rows by an empty tensor once they have been repacked."""
         fallback = layer.weight_type.weight_type
-        gguf_shards = getattr(layer, "gguf_shards", None)
-        if gguf_shards is not None:
-            for idx, shard in gguf_shards.items():
-                wtype = layer.weight_type.shard_weight_type.get(idx, fallback)
-                if wtype in ops.TILE_TYPES and shard.numel() > 0:
-                    tiles[idx] = ops.repack_tiles(shard, shard.shape[0], wtype)
-                    rows[idx] = shard.shape[0]
-                    types[idx] = wtype
-            for idx in tiles:
-                gguf_shards[idx] = torch.empty(0, dtype=torch.uint8, device=tiles[idx].device)
-        elif layer.weight.data.numel() > 0:
-            shard_id = getattr(layer.weight, "shard_id", None)
-            wtypes = ({layer.weight_type.shard_weight_type.get(idx, fallback) for idx in shard_id} if shard_id else {fallback})
-            wtype = next(iter(wtypes))
-            if len(wtypes) == 1 and wtype in ops.TILE_TYPES:
-                w = layer.weight.data
-                tiles["__all__"] = ops.repack_tiles(w, w.shape[0], wtype)
-                rows["__all__"] = w.shape[0]
-                types["__all__"] = wtype
-                layer.weight.data = torch.empty(0, dtype=torch.uint8, device=w.device)
-        if tiles:
-            layer.gguf_tiles = tiles
-            layer.gguf_tiles_rows = rows
-            layer.gguf_tiles_types = types
-            self._create_groups(layer)
+        type_of = lambda sid: layer.weight_type.shard_weight_type.get(sid, fallback)  # noqa: E731
+        shards = getattr(layer, "gguf_shards", None)
+        if shards is not None:
+            def dropper(sid):
+                def drop():
+                    shards[sid] = torch.empty(0, dtype=torch.uint8, device=shards[sid].device)
+                return drop
+            return [(sid, raw, type_of(sid), dropper(sid)) for sid, raw in shards.items()]
+        whole = layer.weight.data
+        sids = getattr(layer.weight, "shard_id", None)
+        kinds = {type_of(sid) for sid in sids} if sids else {fallback}
+        if len(kinds) != 1:
+            return []
+
+        def drop_whole():
+            layer.weight.data = torch.empty(0, dtype=torch.uint8, device=whole.device)
+        return [("__all__", whole, next(iter(kinds)), drop_whole)]
+
+    def _create_tiles(self, layer: torch.nn.Module) -> None:
+        """Load-time repack: every weight tensor of the layer that apply multiplies is turned tile-major once and its
+        raw rows are freed (the reference's step: gguf-tiles-all-types.patch:73-131).  Leaves on the layer
+        gguf_tiles / gguf_tiles_rows / gguf_tiles_types keyed by shard id (or "__all__"), the names the plugin reads."""
+        if self._is_token_embedding(layer):
+            return
+        packed = [(key, ops.repack_tiles(raw, raw.shape[0], wtype), raw.shape[0], wtype, drop)
+                  for key, raw, wtype, drop in self._weight_tensors(layer)
+                  if wtype in ops.TILE_TYPES and raw.numel() > 0]
+        if not packed:
+            return
+        for _, _, _, _, drop in packed:
+            drop()
+        layer.gguf_tiles = {key: tiles for key, tiles, _, _, _ in packed}
+        layer.gguf_tiles_rows = {key: n for key, _, n, _, _ in packed}
+        layer.gguf_tiles_types = {key: wtype for key, _, _, wtype, _ in packed}
+        self._create_groups(layer)
 
     def _create_groups(self, layer: torch.nn.Module) -> None:
-        """Runs of consecutive tiled shards are packed into one buffer with the descriptor tables of the
-        splits a launch can choose; the shards' tiles become views into it
-        (gguf-tiles-grouped.patch:84-115).  groups[first_idx] = (packed, descs, splits, run, nb, block_bytes)."""
-        tiles, rows, types = layer.gguf_tiles, layer.gguf_tiles_rows, layer.gguf_tiles_types
+        """Shards that follow one another in output order and are all tiled form a run: one packed buffer, one launch
+        per call.  groups[first shard of the run] = (packed, descriptor tables, their splits, the run's shard ids, nb,
+        average bytes per 256 weights), the tuple the plugin's apply unpacks (gguf-tiles-grouped.patch:84-115); the
+        shards' tiles become views into the packed buffer."""
+        tiles = layer.gguf_tiles
         if "__all__" in tiles:
-            runs = [["__all__"]]
+            order = ["__all__"]
         else:
-            runs, run = [], []
-            for idx in _gguf_ordered_shard_ids(list(layer.weight.shard_id)):
-                if idx in tiles:
-                    run.append(idx)
-                elif run:
-                    runs.append(run)
-                    run = []
-            if run:
-                runs.append(run)
-        groups = {}
+            order = _gguf_ordered_shard_ids(list(layer.weight.shard_id))
+        # cut the output order wherever a shard is not tiled
+        runs = [list(g) for tiled, g in itertools.groupby(order, key=lambda sid: sid in tiles) if tiled]
+        layer.gguf_groups = {}
         for run in runs:
             packed, views, descs, splits, nb, block_bytes = ops.prepare_grouped_layer(
-                [tiles[i] for i in run], [rows[i] for i in run], [types[i] for i in run])
-            for i, v in zip(run, views):
-                tiles[i] = v
-            groups[run[0]] = (packed, descs, splits, list(run), nb, block_bytes)
-        layer.gguf_groups = groups
+                [tiles[sid] for sid in run], [layer.gguf_tiles_rows[sid] for sid in run], [layer.gguf_tiles_types[sid] for sid in run])
+            tiles.update(zip(run, views))
+            layer.gguf_groups[run[0]] = (packed, descs, splits, run, nb, block_bytes)
+
+    def check_status(self, device=None) -> None:
+        """Raise if any kernel of the path has reported a bounded wait that ran out on the device since the last
+        check (the result of that call was incomplete).  Synchronises; meant for the engine to call between steps."""
+        code = ops.device_status(device, clear=True)
+        if code:
+            raise RuntimeError(f"gq_b200: a kernel reported device status {code} (1: a bounded wait ran out, 2: bad shape) since the last check")
 
     # ---- a6 ----
     def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:

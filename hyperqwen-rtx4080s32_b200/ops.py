@@ -85,6 +85,19 @@ def run_info(wtypes: Sequence[int]) -> int:
     return check(lib().gq_run_info(len(wtypes), _i32_array(wtypes)), "gq_run_info")
 
 
+def device_status(device=None, clear: bool = True) -> int:
+    """The largest status code a kernel of the library reported on the device since it was last cleared (0: none;
+    1: a bounded wait ran out and that call's output is incomplete; 2: bad shape).  Synchronises the stream."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        return check(lib().gq_device_status(1 if clear else 0, torch.cuda.current_stream(dev).cuda_stream), "gq_device_status")
+
+
+def set_peer_wait_limit(seconds: float) -> None:
+    """Time limit of the waits for another GPU's data in the all-reduce kernels (default 4 s)."""
+    check(lib().gq_set_peer_wait_limit_ns(int(seconds * 1e9)), "gq_set_peer_wait_limit_ns")
+
+
 # ---- load time -----------------------------------------------------------------------------------
 
 def repack_tiles(raw: torch.Tensor, n_out: int, wtype: int) -> torch.Tensor:

@@ -23,8 +23,8 @@ _D_OFF = {F.Q4_0: (0,), F.Q5_0: (0,), F.Q8_0: (0,), F.IQ4_NL: (0,), F.Q2_K: (80,
           F.Q4_K: (0, 2), F.Q5_K: (0, 2), F.Q6_K: (208,), F.IQ3_S: (0,), F.IQ4_XS: (0,)}
 
 
-def random_blocks(n_out: int, k: int, wtype: int, seed: int, device="cpu") -> torch.Tensor:
-    """Random valid rows of the type: uniform random bytes, d = U(0.25, 1) * 2^-6, dmin = U(0.25, 1) * 2^-8."""
+def random_blocks(n_out: int, k: int, wtype: int, seed: int, device="cpu", d_exp: int = -6) -> torch.Tensor:
+    """Random valid rows of the type: uniform random bytes, d = U(0.25, 1) * 2^d_exp, dmin = U(0.25, 1) * 2^(d_exp - 2)."""
     wpb, bpb = F.GGML_BLOCK[wtype]
     if k % F.QK:
         raise ValueError(f"K={k} is not a multiple of {F.QK}")
@@ -33,7 +33,7 @@ def random_blocks(n_out: int, k: int, wtype: int, seed: int, device="cpu") -> to
     raw = torch.randint(0, 256, (n_out, nblk, bpb), dtype=torch.uint8, device=device, generator=g)
     for i, off in enumerate(_D_OFF[wtype]):
         u = torch.rand((n_out, nblk), device=device, generator=g) * 0.75 + 0.25
-        val = (u * (2.0 ** -6 if i == 0 else 2.0 ** -8)).to(torch.float16)
+        val = (u * (2.0 ** d_exp if i == 0 else 2.0 ** (d_exp - 2))).to(torch.float16)
         raw[:, :, off:off + 2] = val.view(torch.uint8).reshape(n_out, nblk, 2)
     return raw.reshape(n_out, nblk * bpb)
 

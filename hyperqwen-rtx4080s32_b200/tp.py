@@ -113,8 +113,10 @@ class PushAllReduce:
 class FusedAllReduce:
     """Peer buffers for the fused multiply + all-reduce of the row-parallel layers (gq_gemv_grouped_allreduce): the
     grouped kernel's epilogue exchanges the ranks' bf16 partial outputs and leaves their sum in the output, so a
-    decode step needs no all-reduce launch at all.  One instance serves every row-parallel layer of up to
-    `max_m` rows and `max_n_total` output columns; use it through `ops.fused_allreduce(ctx)`."""
+    decode step needs no all-reduce launch at all.  One instance serves the row-parallel layers of ONE output width
+    (the first call fixes n_total; the library rejects another width on the same buffers, because the exchanged words'
+    positions depend on it) and up to `max_m` rows — in a decoder every row-parallel layer writes the hidden size, so
+    one instance serves the whole model; use it through `ops.fused_allreduce(ctx)`."""
 
     def __init__(self, max_m: int = 64, max_n_total: int = 5120, group=None):
         import ctypes

@@ -171,7 +171,9 @@ int gq_allreduce_push(const void *in_dev, void *out_dev, int64_t n_bytes, int ra
  * gq_gemv_grouped followed by gq_allreduce_push, without the second launch and without fences at system scope.
  * peer_buffers[p] is rank p's buffer of gq_fused_allreduce_buffer_bytes(world, max_m, max_n_total) bytes as seen
  * from this process (peer-mapped, 256-byte aligned, zeroed once before the first call); M <= max_m, n_total <=
- * max_n_total; n_total and every shard's n_out even (status word 2 otherwise); split must be 1 or reduce inside
+ * max_n_total; n_total and every shard's n_out even (status word 2 otherwise); with more than one rank a buffer serves ONE n_total: the first
+ * call fixes it and a call with another is rejected with GQ_ERR_ARG (word positions depend on the width while call
+ * numbers are kept per 16-column unit, so a second width could take a stale word for a current one); split must be 1 or reduce inside
  * the kernel (<= 8); every rank makes the same sequence of calls on a buffer.  No loads from remote memory, no
  * multicast.  Reference: none — the reference has no collective on this path (docs/multi-gpu.md:8-13). */
 int64_t gq_fused_allreduce_buffer_bytes(int world, int64_t max_m, int64_t max_n_total);
@@ -198,6 +200,19 @@ int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const 
 /* Reads the device status word of the last call on this workspace (synchronises the stream): 0, or
  * a positive GQ_DEV_* code (1: a bounded wait ran out). */
 int gq_read_status(const void *workspace_dev, int64_t workspace_bytes, void *stream);
+
+/* The largest device status code any kernel of this library has reported on the current device since the word was
+ * last cleared (synchronises the stream; clear != 0 resets it after reading): 0, or a positive GQ_DEV_* code.  Every
+ * kernel that sets a workspace's status word sets this one too, so a caller that frees its workspace after each call,
+ * or uses the entry point without a workspace argument, still sees a timeout.  Meant to be called between steps.
+ * Reference: none (the reference's kernels have no waits that can run out). */
+int gq_device_status(int clear, void *stream);
+
+/* Time limit, in nanoseconds, of the waits for another GPU's data in gq_allreduce_push and
+ * gq_gemv_grouped_allreduce (default 4 s; 1 us .. 60 s).  Applies to launches made after the call, process-wide.
+ * A wait that runs out sets the status words and leaves y incomplete; the context stays usable.
+ * Reference: none. */
+int gq_set_peer_wait_limit_ns(int64_t ns);
 
 /* Text of the last CUDA runtime error seen by this library in the calling thread ("" if none). */
 const char *gq_last_cuda_error(void);
