@@ -153,6 +153,71 @@ def run_reference(args):
     _emit(json.dumps(line))
 
 
+def gguf_py_sample(m: int):
+    """BASELINE's reference-equivalent CPU path on one tensor: gguf.quants.dequantize to fp32 (numpy), then torch fp32
+    x @ W.T on all host threads; dequantise and multiply timed separately.  One q projection (5120 x 5120, Q4_K)."""
+    import numpy as np
+    import torch
+    from gguf.quants import dequantize
+    from gguf.constants import GGMLQuantizationType
+
+    from hyperqwen_rtx4080s32_b200 import formats as F
+    from hyperqwen_rtx4080s32_b200 import synth
+
+    n_out, k = 5120, 5120
+    raw = synth.random_blocks(n_out, k, F.Q4_K, seed=1).numpy()
+    x = synth.activations(m, k).float()
+    t0 = time.perf_counter()
+    w = torch.from_numpy(np.ascontiguousarray(dequantize(raw, GGMLQuantizationType.Q4_K).reshape(n_out, k)))
+    t1 = time.perf_counter()
+    for _ in range(3):
+        y = x @ w.T
+    t2 = time.perf_counter()
+    mm = (t2 - t1) / 3
+    return {"tensor": "q 5120 x 5120 Q4_K", "raw_bytes": int(raw.size), "dequantize_s": t1 - t0, "matmul_s": mm, "threads": torch.get_num_threads(),
+            "gbs_per_call_dequantise_every_call": raw.size / (t1 - t0 + mm) / 1e9, "gbs_matmul_only_weights_kept_fp32": raw.size / mm / 1e9,
+            "what": "gguf.quants.dequantize (numpy) then torch fp32 x @ W.T, M=%d" % m}
+
+
+def parity_before_timing(st, m, rank, world, dev):
+    """One column-parallel (qkv) and one row-parallel (down, summed over ranks) layer of block 0 against the fp64 oracle
+    on a subset of output columns, through the same calls the timed step makes.  Outside the timed region."""
+    import numpy as np
+    import torch
+
+    from hyperqwen_rtx4080s32_b200 import stack as S
+    from hyperqwen_rtx4080s32_b200 import synth
+    from hyperqwen_rtx4080s32_b200 import tp as _tp
+    from oracle import oracle
+
+    x = st.make_inputs(m)
+    seed = 20261125 % 100000
+    t = st.types[0]
+    errs = {}
+    # column-parallel: this rank's rows of q
+    y = st.layers[0]["qkv"](x["qkv"])
+    n_out, k = st.full_shapes["q"]
+    raw = synth.random_blocks(n_out, k, t["q"], seed=seed + 10 * S.TENSORS.index("q"), device=dev).cpu()    # as the stack draws it
+    if world > 1:
+        raw, _ = _tp.shard_raw(raw, t["q"], "column", rank, world)
+    rows = np.unique(np.concatenate([np.linspace(0, raw.shape[0] - 1, 40).astype(np.int64), [0, 63, raw.shape[0] - 1]]))
+    ref = oracle.matmul_f64(x["qkv"].float().cpu().numpy(), raw[torch.from_numpy(rows)].numpy(), t["q"])
+    errs["qkv"] = float(oracle.rel_err(y[:, torch.from_numpy(rows).to(dev)].float().cpu().numpy(), ref))
+    # row-parallel: down, the sum over ranks against the unsharded layer
+    one = S.LinearStack.__new__(S.LinearStack)
+    one.__dict__.update(st.__dict__)
+    one.layers = st.layers[:1]
+    y = one.step(x)
+    n_out, k = st.full_shapes["down"]
+    raw = synth.random_blocks(n_out, k, t["down"], seed=seed + 10 * S.TENSORS.index("down"), device=dev).cpu()
+    x_full = synth.activations(m, k, seed=100 + m + 7)
+    rows = np.unique(np.concatenate([np.linspace(0, n_out - 1, 40).astype(np.int64), [0, 63, n_out - 1]]))
+    ref = oracle.matmul_f64(x_full.float().numpy(), raw[torch.from_numpy(rows)].numpy(), t["down"])
+    errs["down"] = float(oracle.rel_err(y[:, torch.from_numpy(rows).to(dev)].float().cpu().numpy(), ref))
+    torch.cuda.synchronize()
+    return errs
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -176,10 +241,11 @@ def run_ours(args):
         if not args.nccl_allreduce:
             from hyperqwen_rtx4080s32_b200 import tp as _tp
 
-            _tp.enable_push_all_reduce(max_bytes=max(64, args.m) * 5120 * 2)
+            # the one-shot push all-reduce serves up to 64 rows; larger messages (M = 4096) go to NCCL
+            _tp.enable_push_all_reduce(max_bytes=64 * 5120 * 2)
     L = _lib.lib()
     st = S.LinearStack(n_layers=args.layers, device=dev, tp_rank=rank, tp_size=world)
-    fused = world > 1 and not args.nccl_allreduce and not args.unfused_allreduce and args.m <= 64
+    fused = world > 1 and not args.nccl_allreduce and not args.unfused_allreduce
     if fused:
         try:
             st.enable_fused_all_reduce(max_m=64)
@@ -210,52 +276,13 @@ def run_ours(args):
             print(f"[rank {rank}] fused all-reduce self-check failed: using the separate push kernel", file=sys.stderr, flush=True)
             st.fused_ar = None
             fused = False
-    m = args.m
     st.enable_prefetch(args.l2_prefetch and not args.no_l2_prefetch)
-    x_dev = st.make_inputs(m)
-    x_host = {k: v.cpu().pin_memory() for k, v in x_dev.items()}
-    out_host = torch.empty((m, st.hidden), dtype=torch.bfloat16).pin_memory()
 
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-
-    # warm-up (eager), then capture the step as one CUDA graph
-    for _ in range(max(3, args.warmup)):
-        out = st.step(x_dev)
-    torch.cuda.synchronize()
-    launches0 = L.gq_launch_count()
-    out = st.step(x_dev)
-    torch.cuda.synchronize()
-    launches_per_step = L.gq_launch_count() - launches0
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    captured = 1
-    try:
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
-                out = st.step(x_dev)
-    except Exception as e:   # noqa: BLE001 - a failed capture falls back to eager stepping on every rank
-        captured = 0
-        print(f"[rank {rank}] CUDA graph capture failed, stepping eagerly: {e}", file=sys.stderr, flush=True)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    if world > 1:
-        flag = torch.tensor([captured], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        captured = int(flag.item())
-    if captured:
-        run_step = graph.replay
-    else:
-        def run_step():
-            nonlocal out
-            out = st.step(x_dev)
-    for _ in range(max(3, args.warmup)):
-        run_step()
-    barrier()
 
     def timed(fn, steps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -272,6 +299,59 @@ def run_ours(args):
             ms = float(t.item())
         return ms / steps
 
+    # ---- parity before timing (oracle outside the timed region) ----
+    parity = parity_before_timing(st, args.m, rank, world, dev)
+    if max(parity.values()) >= 1e-2:
+        raise SystemExit(f"[rank {rank}] parity check failed before timing: {parity}")
+
+    side = torch.cuda.Stream()
+
+    def capture_step(m, skip_all_reduce=False):
+        """Warm up, then capture one pass of the stack at M rows as a CUDA graph; returns (replay fn, output, captured, inputs)."""
+        x_dev = st.make_inputs(m)
+        st.skip_all_reduce = skip_all_reduce
+        out = None
+        for _ in range(max(3, args.warmup) if m <= 64 else 1):
+            out = st.step(x_dev)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream())
+        captured = 1
+        try:
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                    out = st.step(x_dev)
+        except Exception as e:   # noqa: BLE001 - a failed capture falls back to eager stepping on every rank
+            captured = 0
+            print(f"[rank {rank}] CUDA graph capture failed at M={m}, stepping eagerly: {e}", file=sys.stderr, flush=True)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if world > 1:
+            flag = torch.tensor([captured], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            captured = int(flag.item())
+        st.skip_all_reduce = False
+        if captured:
+            return graph.replay, out, captured, x_dev, graph
+
+        def eager():
+            st.skip_all_reduce = skip_all_reduce
+            st.step(x_dev)
+            st.skip_all_reduce = False
+        return eager, out, captured, x_dev, None
+
+    # ---- the headline: M = args.m ----
+    m = args.m
+    launches0 = L.gq_launch_count()
+    st.step(st.make_inputs(m))
+    torch.cuda.synchronize()
+    launches_per_step = L.gq_launch_count() - launches0
+    run_step, out, captured, x_dev, _g = capture_step(m)
+    x_host = {k: v.cpu().pin_memory() for k, v in x_dev.items()}
+    out_host = torch.empty((m, st.hidden), dtype=torch.bfloat16).pin_memory()
+    for _ in range(max(3, args.warmup)):
+        run_step()
+    barrier()
     with ClockSampler(local) as clk:
         ms_step = timed(run_step, args.steps)
 
@@ -287,7 +367,8 @@ def run_ours(args):
     h2d = sum(v.numel() * 2 for v in x_host.values())
     d2h = out_host.numel() * 2
 
-    # the grouped kernel alone (activations prepared beforehand): the roofline's launch time
+    # where a step's time goes: the grouped kernel alone (activations prepared beforehand) — the roofline's launch
+    # time —, the activation preparation alone, and (tensor parallel) the step without its all-reduces
     runs = []
     for blk in st.layers:
         for name in ("qkv", "o", "gate_up", "down"):
@@ -302,40 +383,96 @@ def run_ours(args):
                 ws = torch.empty(L.gq_workspace_bytes(m, nb * 256, nt, s), dtype=torch.uint8, device=dev)
                 y = torch.empty((m, nt), dtype=torch.bfloat16, device=dev)
                 runs.append((x_dev[name], packed, descs[splits.index(s)], s, wts, nt, y, ws))
-    for r in runs:
-        ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=1)
-    kgraph = torch.cuda.CUDAGraph()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for r in runs:
-            ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=2)
-        side.synchronize()
-        with torch.cuda.graph(kgraph, stream=side):
-            for r in runs:
-                ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=2)
-    torch.cuda.current_stream().wait_stream(side)
-    for _ in range(3):
-        kgraph.replay()
-    ms_kernel = timed(kgraph.replay, args.steps)
 
-    # the large-batch leg of the metric (prefill TFLOP/s at M = 2048): grouped gate_up, Q4_K, through the op
+    def phase_graph(phases):
+        for r in runs:
+            ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=1)
+        g = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for r in runs:
+                ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=phases)
+            side.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                for r in runs:
+                    ops.grouped_gemm(r[0], r[1], r[2], r[3], r[4], r[5], out=r[6], workspace=r[7], phases=phases)
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            g.replay()
+        return g
+
+    kgraph = phase_graph(2)
+    ms_kernel = timed(kgraph.replay, args.steps)
+    pgraph = phase_graph(1)
+    ms_prep = timed(pgraph.replay, args.steps)
+    del runs, kgraph, pgraph
+    breakdown = {"step_ms": ms_step, "grouped_kernel_only_ms": ms_kernel, "activation_preparation_only_ms": ms_prep}
+    if world > 1:
+        f_noar, *_ = capture_step(m, skip_all_reduce=True)
+        for _ in range(3):
+            f_noar()
+        ms_noar = timed(f_noar, args.steps)
+        breakdown.update({"step_without_all_reduce_ms": ms_noar, "exchange_ms": max(0.0, ms_step - ms_noar),
+                          "all_reduce_share": max(0.0, ms_step - ms_noar) / ms_step})
+
+    # ---- the other batch sizes of the config: BASELINE configs[3] (one GPU) / configs[4] (tensor parallel) ----
+    sweep = {}
+    if not args.no_m_sweep:
+        for mm in ([1, 4, 64] if world == 1 else [1, 64, 4096]):
+            if mm == m:
+                continue
+            f, _o, cap, _x, _gr = capture_step(mm)
+            for _ in range(2):
+                f()
+            ms_mm = timed(f, max(3, args.steps // 2) if mm <= 64 else 3)
+            cell = {"ms_per_step": ms_mm, "gbs": st.raw_bytes_full / (ms_mm * 1e-3) / 1e9, "tokens_per_s": mm / (ms_mm * 1e-3), "cuda_graph": bool(cap)}
+            if world > 1:
+                f2, *_ = capture_step(mm, skip_all_reduce=True)
+                for _ in range(2):
+                    f2()
+                ms2 = timed(f2, max(3, args.steps // 2) if mm <= 64 else 3)
+                cell.update({"step_without_all_reduce_ms": ms2, "all_reduce_share": max(0.0, ms_mm - ms2) / ms_mm,
+                             "all_reduce": "fused into the grouped kernel" if (fused and mm <= 64) else "push kernel" if (mm <= 64 and not args.nccl_allreduce) else "nccl"})
+            sweep[f"M={mm}"] = cell
+            del f, _o, _x, _gr
+            torch.cuda.empty_cache()
+
+    # ---- the large-batch leg of the metric: prefill TFLOP/s, BASELINE configs[2] (grouped gate_up and down, Q4_K and
+    # Q6_K, M = 512 / 2048 / 8192), through the op ----
     prefill = None
     if world == 1 and not args.no_prefill:
         from hyperqwen_rtx4080s32_b200 import formats as F
         from hyperqwen_rtx4080s32_b200 import synth
 
-        pm, pk, pn = 2048, 5120, [17408, 17408]
-        ptiles = [ops.repack_tiles(synth.random_blocks(n, pk, F.Q4_K, seed=900 + i, device=dev), n, F.Q4_K) for i, n in enumerate(pn)]
-        ppacked, pviews, pdescs, psplits, pnb, pbb = ops.prepare_grouped_layer(ptiles, pn, [F.Q4_K, F.Q4_K])
-        del ptiles
-        px = synth.activations(pm, pk, device=dev)
-        pfn = lambda: ops.fused_mul_mat_gguf_tiles_grouped(px, ppacked, pdescs, psplits, pviews, pn, [F.Q4_K, F.Q4_K], pnb, pbb)  # noqa: E731
-        for _ in range(3):
-            pfn()
-        ms_pf = timed(pfn, max(5, args.steps))
-        prefill = {"workload": "grouped gate_up (K 5120, N 2 x 17408), Q4_K, M = 2048 (BASELINE configs[2]); dequantisation not counted",
-                   "tflops": 2.0 * pm * pk * sum(pn) / (ms_pf * 1e-3) / 1e12, "ms": ms_pf, "kernel": "gemm_prefill_kernel<256> (tcgen05, TMEM accumulator)"}
-        del ppacked, pviews, pdescs, px
+        cells = {}
+        for tname in ("Q4_K", "Q6_K"):
+            wt = F.TYPE_IDS[tname]
+            for sname, pn, pk in (("gate_up", [17408, 17408], 5120), ("down", [5120], 17408)):
+                ptiles = [ops.repack_tiles(synth.random_blocks(n, pk, wt, seed=900 + i, device=dev), n, wt) for i, n in enumerate(pn)]
+                ppacked, pviews, pdescs, psplits, pnb, pbb = ops.prepare_grouped_layer(ptiles, pn, [wt] * len(pn))
+                del ptiles
+                for pm in (512, 2048, 8192):
+                    px = synth.activations(pm, pk, device=dev)
+                    pfn = lambda: ops.fused_mul_mat_gguf_tiles_grouped(px, ppacked, pdescs, psplits, pviews, pn, [wt] * len(pn), pnb, pbb)  # noqa: E731
+                    for _ in range(3):
+                        pfn()
+                    ms_pf = timed(pfn, 5)
+                    cells[f"{tname} {sname} M={pm}"] = {"ms": ms_pf, "tflops": 2.0 * pm * pk * sum(pn) / (ms_pf * 1e-3) / 1e12}
+                    del px
+                del ppacked, pviews, pdescs
+                torch.cuda.empty_cache()
+        head = cells["Q4_K gate_up M=2048"]
+        prefill = {"workload": "grouped gate_up (K 5120, N 2 x 17408) and down (K 17408, N 5120), Q4_K and Q6_K, M = 512 / 2048 / 8192 (BASELINE configs[2]); "
+                               "dequantisation not counted in the flops; headline cell: Q4_K gate_up M = 2048",
+                   "tflops": head["tflops"], "ms": head["ms"], "kernel": "gemm_prefill_kernel (tcgen05, TMEM accumulator)", "cells": cells}
+
+    status = ops.device_status(dev)
+    if world > 1:
+        sflag = torch.tensor([status], device=dev)
+        dist.all_reduce(sflag, op=dist.ReduceOp.MAX)
+        status = int(sflag.item())
+    if status != 0:
+        raise SystemExit(f"[rank {rank}] a kernel reported device status {status} during the benchmark: the numbers are void")
 
     if rank == 0:
         peaks, which = measured_peaks()
@@ -343,12 +480,16 @@ def run_ours(args):
             prefill["peak_tflops"] = peaks["bf16_tflops"]
             prefill["frac"] = prefill["tflops"] / peaks["bf16_tflops"]
             prefill["frac_of_sustained"] = prefill["tflops"] / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+            for c in prefill["cells"].values():
+                c["frac"] = c["tflops"] / peaks["bf16_tflops"]
         total_bytes = st.raw_bytes_full
         value = total_bytes / (ms_step * 1e-3) / 1e9
         e2e = total_bytes / (ms_e2e * 1e-3) / 1e9
         achieved = st.raw_bytes_local / (ms_kernel * 1e-3) / 1e9
+        n_launch = 4 * args.layers
         line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32",
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "u8/s8 weights x 16-bit fixed-point activations -> s32, f32 across 256-blocks (M <= 16); f16 x f16 -> f32 above",
                 "data": "synthetic",
                 "config": {"workload": f"mixed-type {args.layers}-layer GGUF decoder linear stack (BASELINE configs[3]{'/[4] tensor-parallel' if world > 1 else ''}), decode M={m}",
                            "bits_per_weight": round(8 * total_bytes / st.weights_full, 3), "raw_block_bytes": total_bytes,
@@ -361,17 +502,26 @@ def run_ours(args):
                 "gpu_launches": int(launches_per_step * args.steps),
                 "roofline": {"bound": "hbm", "kernel": "gemv_grouped_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": achieved / peaks["hbm_gbs"], "peak_source": which, "frac_of_nominal_8TBs": achieved / 8000.0,
-                             "launches_per_step": len(runs), "avg_launch_us": 1e3 * ms_kernel / len(runs),
+                             "launches_per_step": n_launch, "avg_launch_us": 1e3 * ms_kernel / n_launch,
                              # DRAM bytes per launch: ncu captures of single launches of this kernel (profiles/) read
-                             # 1.002-1.009 x the raw block bytes (plus the activation tile from L2); scaled to this
+                             # 1.00-1.01 x the raw block bytes (plus the activation tile from L2); scaled to this
                              # workload's average launch
-                             "traffic": 1.007 * st.raw_bytes_local / len(runs), "algorithmic_bytes_per_launch": st.raw_bytes_local / len(runs)},
+                             "traffic": 1.007 * st.raw_bytes_local / n_launch, "algorithmic_bytes_per_launch": st.raw_bytes_local / n_launch},
+                "breakdown": breakdown,
+                "parity_before_timing": {"max_rel_err_vs_fp64_oracle": parity, "tolerance": 1e-2},
+                "device_status_after_run": status,
                 "clocks": clk.summary()}
+        if sweep:
+            line["other_batch_sizes"] = sweep
         if prefill is not None:
             line["prefill"] = prefill
         if world == 1 and not args.no_cpu:
             v, dt, info = cpu_sample(m, 2, target_s=12.0)
             line["cpu_baseline"] = dict(info, value=v, unit="GB/s")
+            try:
+                line["cpu_baseline_gguf_py"] = gguf_py_sample(m)
+            except Exception as e:   # noqa: BLE001 - the gguf package is test infrastructure; its absence only drops this leg
+                line["cpu_baseline_gguf_py"] = {"unavailable": str(e)}
         _emit(json.dumps(line))
     if world > 1:
         # leave without tearing NCCL down: destroying a process group whose collectives live inside captured
@@ -381,6 +531,147 @@ def run_ours(args):
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+
+# ---- per-type sweeps (the per-type decode sweep of BASELINE configs[1] and the prefill sweep of configs[2]) ----------
+#   python bench.py --sweep decode --types Q4_K Q6_K --shapes gate kv --m 1 8 [--split 1 2] [--eager --iters 3]
+#   python bench.py --sweep prefill --types Q4_K --shapes gate_up down --m 512 2048 8192
+# Decode: for each type x shape x batch the grouped kernel alone (activations prepared beforehand) and the whole call
+# (prepare + kernel + partial sum) as CUDA-graph replays over distinct weight copies totalling more than the L2, median of
+# 7 — the reference's timing method (gguf-plugin/test_gluon_kq_gpu.py:198-245) —, microseconds and GB/s of raw GGUF block
+# bytes.  --eager launches the kernel a few times without a graph (the form a profiler capture wants).
+SHAPES = {"q": (5120, 5120), "kv": (1024, 5120), "o": (5120, 5120), "gate": (17408, 5120), "down": (5120, 17408)}
+
+
+def _graph_time(fn, n: int, reps: int = 7) -> float:
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+        s.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            fn()
+    torch.cuda.current_stream().wait_stream(s)
+    for _ in range(3):
+        g.replay()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return float(np.median(ts)) / n
+
+
+def sweep_prefill(a, dev) -> None:
+    """Grouped gate_up (K 5120, N 2 x 17408) and down (K 17408, N 5120) at prefill batch sizes: milliseconds and
+    TFLOP/s (2 M K N; dequantisation not counted), the whole call (activation layout + the tcgen05 kernel)."""
+    shapes = {"gate_up": ([17408, 17408], 5120), "down": ([5120], 17408), "q": ([5120], 5120)}
+    for tn in a.types:
+        t = F.TYPE_IDS[tn]
+        for sn in [s for s in a.shapes if s in shapes] or ["gate_up", "down"]:
+            n_outs, k = shapes[sn]
+            tiles = [ops.repack_tiles(synth.random_blocks(n, k, t, seed=i, device=dev), n, t) for i, n in enumerate(n_outs)]
+            packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer(tiles, n_outs, [t] * len(n_outs))
+            del tiles
+            d1 = descs[splits.index(1)]
+            n_total = sum(n_outs)
+            for m in a.m:
+                x = synth.activations(m, k, device=dev)
+                y = torch.empty((m, n_total), dtype=torch.bfloat16, device=dev)
+                for _ in range(2):
+                    ops.prefill_gemm(x, packed, d1, n_total, out=y)
+                torch.cuda.synchronize()
+                if a.eager:
+                    _say(f"{tn:7} {sn:8} M={m}: eager", flush=True)
+                    continue
+                ts = []
+                for _ in range(5):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    ops.prefill_gemm(x, packed, d1, n_total, out=y)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1))
+                ms = float(np.median(ts))
+                _say(f"{tn:7} {sn:8} K={k} N={n_total} M={m:5}: {ms:8.3f} ms  {2.0 * m * k * n_total / ms / 1e9:7.1f} TFLOP/s", flush=True)
+            del packed, views, descs
+            torch.cuda.empty_cache()
+
+
+
+
+def run_sweep(a) -> None:
+    import numpy as np  # noqa: F401
+    import torch
+
+    from hyperqwen_rtx4080s32_b200 import _lib, formats as F, ops, synth
+
+    globals().update(np=np, torch=torch, _lib=_lib, F=F, ops=ops, synth=synth)
+    a.types = a.types or list(F.TYPE_IDS)
+    a.m = a.sweep_m or ([1, 8] if a.sweep == "decode" else [512, 2048, 8192])
+    a.shapes = a.shapes or (["q", "kv", "gate", "down"] if a.sweep == "decode" else ["gate_up", "down"])
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    if a.sweep == "prefill":
+        return sweep_prefill(a, dev)
+    for tn in a.types:
+        t = F.TYPE_IDS[tn]
+        for sn in a.shapes:
+            n_out, k = SHAPES[sn] if sn in SHAPES else tuple(int(v) for v in sn.split("x"))   # a name or "NxK"
+            nbytes = F.raw_bytes(t, n_out, k)
+            ncopy = max(2, int(a.copies_mb * 1e6 // nbytes)) if a.copies_mb > 0 else 1
+            packs = []
+            for c in range(ncopy):
+                raw = synth.random_blocks(n_out, k, t, seed=c, device=dev)
+                packs.append(ops.repack_tiles(raw, n_out, t).reshape(-1))
+                del raw
+            nb, n_tiles = k // 256, -(-n_out // 64)
+            if a.copies_mb <= 0:
+                packs = packs * 8        # --copies-mb 0: one copy, replayed eight times per graph (weights stay in L2)
+                ncopy = 8
+            for m in a.m:
+                x = synth.activations(m, k, device=dev)
+                auto = ops.grouped_split_for(n_tiles, nb, m=m, block_bytes=F.BYTES_PER_256[t])
+                cells = []
+                for s in (a.split or [auto]):
+                    if s > nb:
+                        continue
+                    d = torch.from_numpy(ops.build_descs([t], [n_out], k, s)).to(dev)
+                    ws = torch.empty(L.gq_workspace_bytes(m, k, n_out, s), dtype=torch.uint8, device=dev)
+                    y = torch.empty((m, n_out), dtype=torch.bfloat16, device=dev)
+                    ops.grouped_gemm(x, packs[0], d, s, [t], n_out, out=y, workspace=ws, phases=1)
+
+                    def kernel_only():
+                        for p in packs:
+                            ops.grouped_gemm(x, p, d, s, [t], n_out, out=y, workspace=ws, phases=2)
+
+                    def whole_call():
+                        for p in packs:
+                            ops.grouped_gemm(x, p, d, s, [t], n_out, out=y, workspace=ws, phases=7)
+
+                    if a.eager:
+                        for _ in range(a.iters):
+                            kernel_only()
+                        torch.cuda.synchronize()
+                        cells.append(f"S{s}: eager x{a.iters * ncopy}")
+                        continue
+                    us = 1e3 * _graph_time(kernel_only, ncopy)
+                    us_all = 1e3 * _graph_time(whole_call, ncopy)
+                    cells.append(f"S{s}: {us:7.1f} us {nbytes / us / 1e3:6.0f} GB/s (call {us_all:6.1f} us)")
+                _say(f"{tn:7} {sn:5} {n_out}x{k} M={m:2} auto-split={auto} copies={ncopy} | " + " | ".join(cells), flush=True)
+            del packs
+            torch.cuda.empty_cache()
+
+
+
+
+def _say(*parts, flush=True):
+    _emit(" ".join(str(p) for p in parts))
 
 
 def main():
@@ -393,8 +684,17 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill TFLOP/s leg")
+    ap.add_argument("--no-m-sweep", action="store_true", help="skip the other batch sizes of the config (M = 1, 4, 64; tensor parallel: 1, 64, 4096)")
     ap.add_argument("--unfused-allreduce", action="store_true", help="tensor parallel: all-reduce with the library's separate push kernel instead of inside the grouped kernel")
     ap.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: use NCCL for the row-parallel all-reduce instead of the library's push kernel")
+    ap.add_argument("--sweep", choices=["decode", "prefill"], help="per-type sweep instead of the benchmark line (prints a table)")
+    ap.add_argument("--types", nargs="*", default=[], help="--sweep: GGML type names (default all)")
+    ap.add_argument("--shapes", nargs="*", default=[], help="--sweep: q kv o gate down (decode; or NxK), gate_up down q (prefill)")
+    ap.add_argument("--sweep-m", nargs="*", type=int, default=[], help="--sweep: batch sizes")
+    ap.add_argument("--split", nargs="*", type=int, default=[], help="--sweep decode: split-K factors (default: the library's choice)")
+    ap.add_argument("--copies-mb", type=float, default=600.0, help="--sweep decode: megabytes of distinct weight copies per graph (0: one copy, weights stay in L2)")
+    ap.add_argument("--eager", action="store_true", help="--sweep: launch without a CUDA graph (for profiler captures)")
+    ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--l2-prefetch", action="store_true", help="warm the L2 with the next layer's weights from the idle producer lanes (measured neutral)")
     ap.add_argument("--no-l2-prefetch", action="store_true", help="accepted for older command lines; the prefetch is off unless --l2-prefetch is given")
     args = ap.parse_args()
@@ -405,7 +705,9 @@ def main():
     os.dup2(2, 1)
     global _emit
     _emit = lambda text: os.write(json_fd, (text + "\n").encode())
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -98,9 +98,10 @@ class LinearStack:
 
         out = None
         far = getattr(self, "fused_ar", None)
+        exchange = not getattr(self, "skip_all_reduce", False)     # False only to time a step without its all-reduces
         for blk in self.layers:
             for name in ("qkv", "o", "gate_up", "down"):
-                if self.tp_size > 1 and name in ("o", "down"):
+                if self.tp_size > 1 and name in ("o", "down") and exchange:
                     if far is not None:
                         # the all-reduce happens in the grouped kernel's epilogue; a call it cannot serve falls back
                         far.used = False

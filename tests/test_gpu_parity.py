@@ -403,7 +403,7 @@ def test_fused_all_reduce_single_rank_degenerate():
 def test_push_all_reduce_single_rank_degenerate(gq_lib):
     """The push all-reduce kernel with a world of one (its own buffer is the only peer): the result is the input,
     the per-CTA call counters advance, the slot sets alternate, and a replayed CUDA graph keeps working.  The
-    multi-rank exchange itself is checked on several GPUs by `python -m hyperqwen_rtx4080s32_b200.tp_check`."""
+    multi-rank exchange itself is checked on several GPUs by tests/test_multi_gpu.py."""
     import ctypes
 
     max_bytes = 64 * 5120 * 2

@@ -1,13 +1,13 @@
-"""Multi-GPU check of the push all-reduce against NCCL, one process per GPU:
+"""Worker of tests/test_multi_gpu.py: the multi-GPU checks, one process per GPU:
 
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
-        -m hyperqwen_rtx4080s32_b200.tp_check
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P tests/tp_worker.py
 
 Every rank all-reduces seeded bf16 vectors of several sizes with both paths (the push kernel sums in fp32 in
 rank order and rounds once; NCCL's result may differ in the last bf16 bit), repeatedly, eagerly and from a
 replayed CUDA graph, and times both; then a two-block tensor-parallel stack runs with the all-reduce fused into
-the grouped kernel and with the separate push kernel, which must agree bit for bit.  Exits non-zero on a mismatch
-or a device timeout status.
+the grouped kernel and with the separate push kernel, which must agree bit for bit and must match the fp64 oracle of
+the unsharded layer; a fused-exchange buffer refuses a second output width.  Exits non-zero on a mismatch or a device
+status other than 0.
 """
 from __future__ import annotations
 
@@ -15,10 +15,16 @@ import datetime
 import os
 import sys
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
-from . import tp
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from hyperqwen_rtx4080s32_b200 import _lib, ops, synth, tp  # noqa: E402
+from oracle import oracle  # noqa: E402
 
 
 def main() -> int:
@@ -72,7 +78,7 @@ def main() -> int:
             print(f"{name}: {1e3 * e0.elapsed_time(e1) / (5 * len(bufs)):.2f} us per all-reduce of {x.numel() * 2} bytes over {world} GPUs (graph replay)", flush=True)
     # fused multiply + all-reduce against the unfused path (grouped kernel, then the push all-reduce): the same
     # bf16 partial outputs summed in the same order, so the results must be bit-identical
-    from . import formats as F, stack as S
+    from hyperqwen_rtx4080s32_b200 import formats as F, stack as S
 
     types = [{"q": F.Q4_K, "k": F.Q4_K, "v": F.Q4_K, "o": F.IQ4_XS, "gate": F.Q2_K, "up": F.Q2_K, "down": F.Q6_K},
              {"q": F.IQ3_S, "k": F.Q8_0, "v": F.Q3_K, "o": F.Q5_K, "gate": F.IQ3_S, "up": F.Q3_K, "down": F.Q4_K}]
@@ -96,6 +102,20 @@ def main() -> int:
             if not torch.equal(a, b) or torch.isnan(b).any():
                 ok = False
                 print(f"[rank {rank}] fused all-reduce differs from the unfused path at M={m}: max diff {(a.float() - b.float()).abs().max().item()}", flush=True)
+        # against the oracle of the unsharded layer: the step returns the last block's down projection, summed over ranks
+        # (each rank's partial output is rounded to bf16 before the sum: `world` roundings instead of one)
+        n_out, k = stk.full_shapes["down"]
+        t_down = types[-1]["down"]
+        raw = synth.random_blocks(n_out, k, t_down, seed=20261125 % 100000 + 1000 * (len(types) - 1) + 10 * S.TENSORS.index("down"),
+                                  device=dev).cpu()      # drawn on the device, as the stack draws it
+        x_full = synth.activations(m, k, seed=100 + m + 7)
+        rows = np.unique(np.concatenate([np.linspace(0, n_out - 1, 48).astype(np.int64), [0, 63, 64, n_out - 1]]))
+        ref = oracle.matmul_f64(x_full.float().numpy(), raw[torch.from_numpy(rows)].numpy(), t_down)
+        got = outs["fused"][0][:, torch.from_numpy(rows).to(dev)].float().cpu().numpy()
+        err = oracle.rel_err(got, ref)
+        if not err < 6e-3 * (1 + 0.5 * (world - 1)):
+            ok = False
+            print(f"[rank {rank}] tensor-parallel down projection against the oracle at M={m}: rel err {err:.3e}", flush=True)
     # ... and replayed from a CUDA graph
     xin = stk.make_inputs(8)
     stk.fused_ar = stk._far
@@ -114,14 +134,28 @@ def main() -> int:
     if not torch.equal(got, want):
         ok = False
         print(f"[rank {rank}] fused all-reduce: graph replay differs", flush=True)
-    st = fast.status()
+    # a fused-exchange buffer is bound to the output width it was first used with
+    lin_small = S.GGUFLinear(1024, [256])
+    lin_small.load_shard(synth.random_blocks(256, 1024, F.Q4_K, seed=5).to(dev), F.Q4_K)
+    lin_small.finalize()
+    try:
+        with ops.fused_allreduce(stk._far):
+            stk._far.used = False
+            lin_small(synth.activations(8, 1024, device=dev))
+        refused = False
+    except _lib.GqError:
+        refused = True
+    if not refused:
+        ok = False
+        print(f"[rank {rank}] a second output width on one fused all-reduce buffer was not refused", flush=True)
+    st = max(fast.status(), ops.device_status(dev))
     if st != 0:
         ok = False
         print(f"[rank {rank}] device status {st}", flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print("tp_check", "ok" if int(flag.item()) else "FAILED", flush=True)
+        print("tp_worker", "ok" if int(flag.item()) else "FAILED", flush=True)
     dist.barrier()
     torch.cuda.synchronize()
     sys.stdout.flush()
