@@ -235,7 +235,9 @@ __host__ __device__ inline int64_t align256(int64_t v) { return (v + 255) & ~(in
 // After the rows of a k-block come their scales 2^-e (fp32, one per batch row, padded to a multiple of 16 bytes).
 #define GQ_X8_ROW 576
 #define GQ_X8_SUMS 512
+#ifndef GQ_GEMV8_MAX_ROWS
 #define GQ_GEMV8_MAX_ROWS 16      // up to here the integer form runs; above it the fp16 form
+#endif
 
 __host__ __device__ inline int gq_x8_tile_bytes(int M) { return M * GQ_X8_ROW + ((4 * M + 15) & ~15); }
 
@@ -1350,7 +1352,7 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     {
         // ring depth: four stages when four CTAs of them still fit an SM's shared memory, else three (swept on the
         // 64-layer stack: deeper rings with fewer resident CTAs were slower overall)
-        const int xb = mt == 1 ? gq_stage_xbytes<1, 1>() : mt == 2 ? gq_stage_xbytes<2, 1>() : 8 * mt * GQ_XROW_BYTES;
+        const int xb = !form ? 8 * mt * GQ_XROW_BYTES : mt == 1 ? gq_stage_xbytes<1, 1>() : mt == 2 ? gq_stage_xbytes<2, 1>() : gq_stage_xbytes<4, 1>();
         const int stage_bytes = p.wbytes_max + xb;
         // (an SM has 228 KB of shared memory and the system keeps 1 KB of it per resident CTA)
         const int fixed = 64 + (p.has_iq3s ? (form ? GQ_IQ3S8_SMEM_BYTES : GQ_IQ3S_SMEM_BYTES) : 0) + 1024, red1 = GQ_CONSUMER_WARPS * mt * 512;
@@ -1369,7 +1371,7 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         switch (mt) {
             case 1: rc = launch_gemv8_m8(p, n_desc, st, (run_info >> 17) & 31); break;
             case 2: rc = launch_gemv<2, 3, 1, 0>(p, n_desc, st); break;
-            case 4: rc = launch_gemv<4, 2, 0, 0>(p, n_desc, st); break;
+            case 4: rc = form ? launch_gemv<4, 2, 1, 0>(p, n_desc, st) : launch_gemv<4, 2, 0, 0>(p, n_desc, st); break;
             default: rc = launch_gemv<8, 0, 0, 0>(p, n_desc, st); break;
         }
     }
@@ -1588,56 +1590,102 @@ extern "C" int gq_allreduce_push(const void *in_dev, void *out_dev, int64_t n_by
 // ---- prefill ----------------------------------------------------------------------------------------
 static int prefill_nb(int64_t M) { return M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
-static int64_t pf_ws_layout(int64_t M, int64_t K, int nbt, void *base, int **status, float **ex, uint8_t **xp) {
+// Split-K of a prefill launch: one CTA per (pair of 64-row tiles, NB batch rows) is resident per SM, so a launch of
+// few CTAs (o / down / qkv at a few hundred rows) leaves SMs idle; its k-blocks are then cut into S balanced parts
+// (grid.z), S chosen to minimise waves x (k-blocks per CTA + a fixed cost per wave).  Larger launches keep S = 1.
+static int prefill_split(int64_t n_desc, int64_t M, int64_t nb, int nbt, int sms) {
+    const int64_t ctas = ((n_desc + 1) / 2) * ((M + nbt - 1) / nbt);
+    if (sms <= 0) sms = 148;
+    if (nbt <= 64) sms *= 2;       // the 64-row variant is built for two CTAs per SM
+    int best = 1;
+    double best_cost = 1e300;
+    // the fp32 partials cost a write and a read of S x M x n_total x 4 bytes: worth it only while a launch fills less than
+    // half of the GPU (measured: down at 512 rows, 80 CTAs on 148 SMs, gains nothing from a split; at 64 rows it halves)
+    if (ctas * 2 > sms) return 1;
+    for (int S = 1; S <= 8 && (int64_t)S * 4 <= nb; ++S) {
+        const int64_t waves = (ctas * S + sms - 1) / sms;
+        const double cost = (double)waves * ((double)nb / S + 6.0) + (S > 1 ? 2.0 : 0.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = S; }
+    }
+    return best;
+}
+
+static int device_sms() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int v = cached[dev].load();
+    if (v <= 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev].store(v);
+    }
+    return v;
+}
+
+static int64_t pf_ws_layout(int64_t M, int64_t K, int nbt, int split, int64_t n_total, void *base, int **status, float **ex, uint8_t **xp,
+                            float **partials) {
     const int64_t mt = (M + nbt - 1) / nbt;
     int64_t off = 256;
     const int64_t o_ex = off; off = align256(off + M * 4);
     off = (off + 1023) & ~(int64_t)1023;
     const int64_t o_xp = off; off += mt * nbt * K * 2;
-    if (base) { uint8_t *b = (uint8_t *)base; *status = (int *)b; *ex = (float *)(b + o_ex); *xp = b + o_xp; }
+    const int64_t o_p = off; if (split > 1) off = align256(off + (int64_t)split * M * n_total * 4);
+    if (base) { uint8_t *b = (uint8_t *)base; *status = (int *)b; *ex = (float *)(b + o_ex); *xp = b + o_xp; *partials = (float *)(b + o_p); }
     return off;
 }
 
-extern "C" int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K) {
-    if (M < 0 || K <= 0 || K % GQ_QK) return GQ_ERR_SHAPE;
-    return pf_ws_layout(M, K, prefill_nb(M), nullptr, nullptr, nullptr, nullptr);
+extern "C" int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K, int64_t n_total, int64_t n_desc) {
+    if (M < 0 || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0) return GQ_ERR_SHAPE;
+    const int nbt = prefill_nb(M);
+    return pf_ws_layout(M, K, nbt, prefill_split(n_desc, M, K / GQ_QK, nbt, device_sms()), n_total, nullptr, nullptr, nullptr, nullptr, nullptr);
 }
 
 template <int NB>
-static int launch_prefill(const PrefillParams &p, const __nv_bfloat16 *x, int64_t ldx, float *ex, uint8_t *xp, cudaStream_t st) {
+static int launch_prefill(PrefillParams &p, const __nv_bfloat16 *x, int64_t ldx, float *ex, uint8_t *xp, cudaStream_t st) {
     const int mt = (p.M + NB - 1) / NB;
     const size_t smem = 1024 + (size_t)GQ_PF_STAGES * (GQ_PF_A_BYTES + NB * 128) + 128 + GQ_IQ3S_SMEM_BYTES;
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
-        GQ_CUDA(cudaFuncSetAttribute(gemm_prefill_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        GQ_CUDA(cudaFuncSetAttribute(gemm_prefill_kernel<NB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        GQ_CUDA(cudaFuncSetAttribute(gemm_prefill_kernel<NB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev < 64) done_mask.fetch_or(1ull << dev);
     }
     prep_x_prefill_kernel<NB><<<(unsigned)(mt * NB), 256, 0, st>>>(x, ldx, p.K, p.M, ex, xp, p.status);
     GQ_LAUNCHED();
-    gemm_prefill_kernel<NB><<<dim3((unsigned)((p.n_desc + 1) / 2), (unsigned)mt), GQ_PF_THREADS, smem, st>>>(p);
+    if (p.split > 1) gemm_prefill_kernel<NB, true><<<dim3((unsigned)((p.n_desc + 1) / 2), (unsigned)mt, (unsigned)p.split), GQ_PF_THREADS, smem, st>>>(p);
+    else gemm_prefill_kernel<NB, false><<<dim3((unsigned)((p.n_desc + 1) / 2), (unsigned)mt), GQ_PF_THREADS, smem, st>>>(p);
     GQ_LAUNCHED();
+    if (p.split > 1) {
+        const int64_t n = (int64_t)p.M * p.n_total;
+        sum_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.partials, p.split, p.M, p.n_total, p.y, p.ldy);
+        GQ_LAUNCHED();
+    }
     return GQ_OK;
 }
 
 extern "C" int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
-                               int64_t n_desc, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev, int64_t workspace_bytes,
-                               void *stream) {
+                               int64_t n_desc, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
+                               int64_t workspace_bytes, void *stream) {
     if (M < 0 || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0) return GQ_ERR_SHAPE;
     if (M == 0 || n_total == 0 || n_desc == 0) return GQ_OK;
     if (!x_dev || !packed_dev || !desc_dev || !y_dev || !workspace_dev) return GQ_ERR_ARG;
     if (((uintptr_t)packed_dev & 15) || ((uintptr_t)workspace_dev & 1023) || ((uintptr_t)x_dev & 15) || (ldx & 7) || ldx < K || ldy < n_total)
         return GQ_ERR_ARG;
     if (n_desc > 0x7ffffffe || M > (int64_t)65535 * 64) return GQ_ERR_LIMIT;
+    const int maxb = run_info & 0xFFFF;
+    if (maxb < 84 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
     const int nbt = prefill_nb(M);
-    int *status; float *ex; uint8_t *xp;
-    const int64_t need = pf_ws_layout(M, K, nbt, workspace_dev, &status, &ex, &xp);
+    const int split = prefill_split(n_desc, M, K / GQ_QK, nbt, device_sms());
+    int *status; float *ex; uint8_t *xp; float *partials;
+    const int64_t need = pf_ws_layout(M, K, nbt, split, n_total, workspace_dev, &status, &ex, &xp, &partials);
     if (workspace_bytes < need) return GQ_ERR_WORKSPACE;
     if (int rc = ensure_tables()) return rc;
     PrefillParams p;
     p.packed = (const uint8_t *)packed_dev; p.desc = desc_dev; p.n_desc = (int)n_desc; p.xp = xp; p.ex = ex;
     p.y = (__nv_bfloat16 *)y_dev; p.ldy = ldy; p.M = (int)M; p.K = (int)K; p.nb = (int)(K / GQ_QK); p.status = status;
+    p.split = split; p.partials = partials; p.n_total = n_total;
     cudaStream_t st = (cudaStream_t)stream;
     switch (nbt) {
         case 64: return launch_prefill<64>(p, (const __nv_bfloat16 *)x_dev, ldx, ex, xp, st);

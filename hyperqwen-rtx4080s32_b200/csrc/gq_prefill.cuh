@@ -12,6 +12,11 @@
 //               them into the K-major swizzled A stage; afterwards they drain the accumulator (tcgen05.ld),
 //               apply the activation row scale and store bf16.
 // Weights sit on the MMA's M side (D rows = output features), batch rows on N, as in the small-batch kernel.
+// With a split-K factor S > 1 (grid.z; for launches that would otherwise leave SMs without a CTA) a CTA walks one
+// balanced part of the k-blocks and stores fp32 partial outputs, which sum_partials_kernel adds in split order.
+// (Streaming the packed tiles through a shared-memory ring with bulk copies instead of loading them straight into
+// registers one k-block ahead was measured 8-15 % slower at every batch size: the ring costs an A / B stage at 256
+// batch rows, and the loads from it sit at the head of every k-block instead of overlapping the previous one.)
 // Every wait is bounded; a wait that runs out sets the status word, and the CTA still frees its tensor memory.
 #pragma once
 #include "gq_decode.cuh"
@@ -34,6 +39,9 @@ struct PrefillParams {
     int64_t ldy;
     int M, K, nb;
     int *status;
+    int split;                // split-K factor (grid.z); > 1: fp32 partials instead of y
+    float *partials;          // [split][M][n_total]
+    int64_t n_total;
 };
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -100,7 +108,7 @@ __device__ __forceinline__ void pf_store_pair(const Dec<TYPE> &dec, uint8_t *a_s
 
 // the dequantiser loop of one warp for a tile of TYPE: for every k-block, four k-slices through the stage ring
 template <int TYPE>
-__device__ __forceinline__ bool pf_dequant(const uint8_t *tile_base, int slab, int row0, int nb, uint8_t *smem_a0, int stage_bytes,
+__device__ __forceinline__ bool pf_dequant(const uint8_t *tile_base, int slab, int row0, int nb, uint8_t *smem_a0, int stage_bytes,   // tile_base: first k-block of this CTA's part
                                            uint64_t *a_full, uint64_t *freeb, const DecAux &aux, int lane) {
     const int Bt = gq_type_bytes(TYPE);
     const int g = lane >> 2, t = lane & 3;
@@ -139,8 +147,8 @@ __device__ __forceinline__ bool pf_idle(int nb, uint64_t *a_full, uint64_t *free
     return true;
 }
 
-template <int NB>
-__global__ void __launch_bounds__(GQ_PF_THREADS, 1) gemm_prefill_kernel(const PrefillParams p) {
+template <int NB, bool SPLITK>
+__global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_kernel(const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // layout: [stages x (A 16 KB | B NB*128)] [barriers] [tmem slot] [IQ3_S grid 4 KB]
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -154,8 +162,9 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, 1) gemm_prefill_kernel(const Pr
     uint2 *grid_s = reinterpret_cast<uint2 *>(smem + GQ_PF_STAGES * STAGE + 128);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pair = blockIdx.x, mt = blockIdx.y;
-    const int nslices = 4 * p.nb;
+    const int pair = blockIdx.x, mt = blockIdx.y, z = SPLITK ? (int)blockIdx.z : 0;
+    const int kb0 = SPLITK ? (int)(((int64_t)z * p.nb) / p.split) : 0, kb1 = SPLITK ? (int)(((int64_t)(z + 1) * p.nb) / p.split) : p.nb;
+    const int nkb = kb1 - kb0, nslices = 4 * nkb;
 
     // the two 64-row tiles of this CTA
     const int32_t *d0 = p.desc + (int64_t)(2 * pair) * GQ_DESC_WORDS;
@@ -194,7 +203,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, 1) gemm_prefill_kernel(const Pr
     if (warp == 0) {
         // ---- activation producer ----
         if (lane == 0) {
-            const uint8_t *src = p.xp + (int64_t)mt * (p.K / 64) * B_BYTES;
+            const uint8_t *src = p.xp + ((int64_t)mt * (p.K / 64) + 4 * (int64_t)kb0) * B_BYTES;
             for (int i = 0, st = 0, round = 0; i < nslices; ++i) {
                 if (round > 0 && !mbar_wait(freeb + st, (round - 1) & 1)) { ok = false; break; }
                 mbar_expect_tx(b_full + st, B_BYTES);
@@ -234,11 +243,11 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, 1) gemm_prefill_kernel(const Pr
             aux.iq4 = {tb[0], tb[1], tb[2], tb[3]};
         }
         if (slab >= 4 && !has1) {
-            ok = pf_idle(p.nb, a_full, freeb, lane);
+            ok = pf_idle(nkb, a_full, freeb, lane);
         } else {
-            const uint8_t *tile_base = p.packed + (int64_t)dd[0] * 16;
+            const uint8_t *tile_base = p.packed + (int64_t)dd[0] * 16 + (int64_t)kb0 * 64 * gq_type_bytes(dd[1]);
             const int sl = slab & 3, row0 = 16 * slab;
-#define GQ_PF(T) case T: ok = pf_dequant<T>(tile_base, sl, row0, p.nb, smem, STAGE, a_full, freeb, aux, lane); break;
+#define GQ_PF(T) case T: ok = pf_dequant<T>(tile_base, sl, row0, nkb, smem, STAGE, a_full, freeb, aux, lane); break;
             switch (dd[1]) {
                 GQ_PF(GQ_Q4_0) GQ_PF(GQ_Q5_0) GQ_PF(GQ_Q8_0) GQ_PF(GQ_Q2_K) GQ_PF(GQ_Q3_K) GQ_PF(GQ_Q4_K)
                 GQ_PF(GQ_Q5_K) GQ_PF(GQ_Q6_K) GQ_PF(GQ_IQ4_NL) GQ_PF(GQ_IQ3_S) GQ_PF(GQ_IQ4_XS)
@@ -272,7 +281,11 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, 1) gemm_prefill_kernel(const Pr
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int n = mt * NB + c0 + j;
-                    if (row_ok && n < p.M) p.y[(int64_t)n * p.ldy + col] = __float2bfloat16_rn(__uint_as_float(v[j]) * p.ex[n]);
+                    if (row_ok && n < p.M) {
+                        const float val = __uint_as_float(v[j]) * p.ex[n];
+                        if constexpr (SPLITK) p.partials[((int64_t)z * p.M + n) * p.n_total + col] = val;
+                        else p.y[(int64_t)n * p.ldy + col] = __float2bfloat16_rn(val);
+                    }
                 }
             }
         }

@@ -20,10 +20,8 @@ from . import formats as F
 from ._lib import DESC_WORDS, MAX_GEMV_ROWS, GqError, check, lib
 
 TILE_TYPES = F.SUPPORTED_TYPES   # every one of the eleven types is held tile-major (the reference: GLUON_TILE_TYPES)
-GEMV_MAX_ROWS = MAX_GEMV_ROWS    # row-count dispatch threshold: above it the prefill kernel takes over
-WIDE_MIN_ROWS = 32               # above it the small-batch path runs as two launches of at most 32 rows
-WIDE_PREFILL_ROWS = 40           # ... and above this one a run of at least two tiles per SM goes to the prefill kernel already
-
+GEMV_MAX_ROWS = MAX_GEMV_ROWS    # the grouped kernel's own limit (the C ABI accepts up to 64 rows)
+DECODE_MAX_ROWS = 32             # row-count dispatch threshold: above it the tcgen05 kernel takes over
 
 def _stream_ptr(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
@@ -256,9 +254,10 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
     return out
 
 
-def prefill_gemm(x: torch.Tensor, packed: torch.Tensor, desc1: torch.Tensor, n_total: int, out: torch.Tensor | None = None) -> torch.Tensor:
+def prefill_gemm(x: torch.Tensor, packed: torch.Tensor, desc1: torch.Tensor, n_total: int, out: torch.Tensor | None = None,
+                 wtypes: Sequence[int] | None = None) -> torch.Tensor:
     """The large-batch path (tcgen05 dequant-GEMM): x bf16 [M, K] -> out bf16 [M, n_total]; desc1 is the run's
-    split-1 descriptor table."""
+    split-1 descriptor table; wtypes the run's GGML types (sizes the packed-tile ring; all eleven assumed if absent)."""
     _need_cuda(x, "x")
     if x.dtype != torch.bfloat16 or x.dim() != 2:
         raise GqError(f"x must be bf16 [M, K], got {x.dtype} {tuple(x.shape)}")
@@ -272,11 +271,13 @@ def prefill_gemm(x: torch.Tensor, packed: torch.Tensor, desc1: torch.Tensor, n_t
     if m == 0 or n_total == 0:
         return out
     L = lib()
-    ws_bytes = check(L.gq_prefill_workspace_bytes(m, k), "gq_prefill_workspace_bytes")
+    with torch.cuda.device(x.device):
+        ws_bytes = check(L.gq_prefill_workspace_bytes(m, k, n_total, int(desc1.shape[0])), "gq_prefill_workspace_bytes")
     ws = torch.empty(ws_bytes + 1024, dtype=torch.uint8, device=x.device)
     base = (ws.data_ptr() + 1023) // 1024 * 1024
+    info = run_info(wtypes) if wtypes else 272
     with torch.cuda.device(x.device):
-        check(L.gq_gemm_prefill(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc1.data_ptr(), int(desc1.shape[0]), out.data_ptr(),
+        check(L.gq_gemm_prefill(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc1.data_ptr(), int(desc1.shape[0]), info, out.data_ptr(),
                                 out.stride(0), n_total, base, ws_bytes, _stream_ptr(x)), "gq_gemm_prefill")
     return out
 
@@ -285,38 +286,28 @@ def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[tor
                           tiles: list[torch.Tensor], n_outs: list[int], weight_types: list[int], nb: int, block_bytes: int) -> torch.Tensor:
     """A layer's run of shards in one call: x bf16 [M, K] -> [M, sum(n_outs)] (reference:
     gluon_mul_mat_tiles_grouped, gguf-plugin/gluon/interface.py:141-188).  The row-count dispatch lives
-    here, inside the op: up to 64 rows one grouped launch at the split of the table for that row count
-    (33..64 rows as two launches; up to 40 rows for runs of at least two tiles per SM); above, the tcgen05 dequant-GEMM (weights
-    dequantised into shared memory once per 256 batch rows)."""
+    here, inside the op: up to 32 rows one grouped launch at the split of the table for that row count; above, the
+    tcgen05 dequant-GEMM (weights dequantised into shared memory once per 64, 128 or 256 batch rows)."""
     m = int(x.shape[0])
     n_total = sum(int(n) for n in n_outs)
     out = torch.empty((m, n_total), dtype=x.dtype, device=x.device)
     if m == 0:
         return out
     n_tiles = sum(-(-int(n) // 64) for n in n_outs)
-    # 41..64 rows: a run wide enough to give every SM a CTA of the tcgen05 kernel (two tiles each) is faster on it
-    # than on the grouped kernel (gate_up: 110 us against 116 us for two 32-row launches, 140 us for one 64-row launch;
-    # measured on the mixed stack: the grouped kernel wins at 33 rows, the tcgen05 kernel at 48)
-    wide = m > WIDE_PREFILL_ROWS and n_tiles >= 2 * sm_count(x.device)
-    if m <= GEMV_MAX_ROWS and not wide:
+    # up to 32 rows the grouped kernel streams the weights once per 8 (integer form, to 16 rows) or 32 (fp16 form) rows;
+    # from 33 rows the tcgen05 kernel (64-row variant, two CTAs per SM, split-K on narrow layers) dequantises each weight
+    # once for all rows and is faster on every layer of the stack (gate_up at 64 rows: 79 us against 116 us for two
+    # 32-row launches of the grouped kernel; down: 58 against 84)
+    if m <= DECODE_MAX_ROWS:
         s = grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=sm_count(x.device))
         if s not in desc_splits:
             s = 1
         ar = _FUSED_AR
         if ar is not None and not (m <= ar.max_m and n_total <= ar.max_n_total and s <= 8 and all(int(n) % 2 == 0 for n in n_outs)):
             ar = None
-        d = descs[desc_splits.index(s)]
-        if m > WIDE_MIN_ROWS:
-            # 33..64 rows: 32 rows and the rest in two launches beat one launch of the 64-row form (whose 39 KB
-            # activation tile per k-block leaves one CTA per SM); the second pass finds most of the weights in L2.
-            # Rows are independent, so the result is the same either way.
-            h = WIDE_MIN_ROWS
-            grouped_gemm(x[:h], packed, d, s, weight_types, n_total, out=out[:h], allreduce=ar)
-            grouped_gemm(x[h:], packed, d, s, weight_types, n_total, out=out[h:], allreduce=ar)
-            return out
-        grouped_gemm(x, packed, d, s, weight_types, n_total, out=out, allreduce=ar)
+        grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, out=out, allreduce=ar)
         return out
-    prefill_gemm(x, packed, descs[desc_splits.index(1)], n_total, out=out)
+    prefill_gemm(x, packed, descs[desc_splits.index(1)], n_total, out=out, wtypes=weight_types)
     return out
 
 

@@ -182,20 +182,24 @@ int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K, int64_t l
                               int64_t workspace_bytes, int rank, int world, const uint64_t *peer_buffers, int64_t max_m,
                               int64_t max_n_total, void *stream);
 
-/* Workspace bytes of gq_gemm_prefill for a batch of M rows (activations re-laid out for the tensor-core
- * operand, row scales, status). */
-int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K);
+/* Workspace bytes of gq_gemm_prefill for a batch of M rows, a run of n_desc tiles and n_total output columns
+ * (activations re-laid out for the tensor-core operand, row scales, status, and fp32 partial outputs when the call
+ * will split K).  Depends on the current device's SM count. */
+int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K, int64_t n_total, int64_t n_desc);
 
 /* Y[M, n_total] = X[M, K] . W^T for a run of packed shards at any M (meant for M > GQ_MAX_GEMV_ROWS): the
- * large-batch path.  desc_dev is the run's descriptor table built with split = 1 (one row per 64-row tile).
- * Each CTA dequantises two tiles' k-slices into shared memory as fp16 and feeds tcgen05.mma with the fp32
- * accumulator in tensor memory; the dequantised weights never reach HBM.  workspace_dev: at least
- * gq_prefill_workspace_bytes(M, K) bytes, 1024-byte aligned; x_dev 16-byte aligned with ldx a multiple of 8.
+ * large-batch path.  desc_dev is the run's descriptor table built with split = 1 (one row per 64-row tile); run_info is
+ * gq_run_info of the run's types (sizes the packed-tile ring in shared memory).
+ * Each CTA streams two tiles' packed k-blocks through a shared-memory ring (bulk copies), dequantises them into a
+ * second ring as fp16 and feeds tcgen05.mma with the fp32 accumulator in tensor memory; the dequantised weights never
+ * reach HBM.  A launch too small to give every SM a CTA splits K over grid.z and a second launch adds the fp32 partial
+ * outputs in split order.  workspace_dev: at least gq_prefill_workspace_bytes(M, K, n_total, n_desc) bytes, 1024-byte
+ * aligned; x_dev 16-byte aligned with ldx a multiple of 8.
  * Reference: the wide forms (bm 64 / 128) and the dequantise + cuBLAS path of gluon_mul_mat_tiles_grouped
  * (gguf-plugin/gluon/interface.py:159-188), dequantize_tiles (gguf-plugin/gluon/tiles.py:141-149). */
 int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
-                    int64_t n_desc, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev, int64_t workspace_bytes,
-                    void *stream);
+                    int64_t n_desc, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
+                    int64_t workspace_bytes, void *stream);
 
 /* Reads the device status word of the last call on this workspace (synchronises the stream): 0, or
  * a positive GQ_DEV_* code (1: a bounded wait ran out). */

@@ -317,26 +317,26 @@ def test_prefill_mixed_run_and_dispatch_boundary():
                 col += n
 
 
-def test_wide_run_dispatch_takes_the_tcgen05_path_from_41_rows():
-    """A run of at least two tiles per SM goes to the tcgen05 kernel already at 41..64 rows: same tolerance, and
-    bit-identical to calling that kernel directly; up to 40 rows it is still the grouped kernel (two launches above 32)."""
-    n_out, k, t = 64 * 2 * ops.sm_count(dev()), 512, F.Q4_K
-    raw = synth.random_blocks(n_out, k, t, seed=77)
-    tl = ops.repack_tiles(raw.to(dev()), n_out, t)
-    packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer([tl], [n_out], [t])
-    d1 = descs[splits.index(1)]
-    for m in (32, 33, 40, 41, 64):
-        x = synth.activations(m, k, device=dev())
-        y = ops.fused_mul_mat_gguf_tiles_grouped(x, packed, descs, splits, views, [n_out], [t], nb, bb)
-        assert oracle.rel_err(y.float().cpu().numpy(), ref_gemm(x, raw, t)) < TOL_TIGHT
-        same = torch.equal(y, ops.prefill_gemm(x, packed, d1, n_out))
-        assert same == (m > 40)
-        if 32 < m <= 40:      # two launches of the grouped kernel: 32 rows in the fp16 form, the rest in the integer form
-            s = ops.grouped_split_for(n_out // 64, nb, m=m, block_bytes=bb, sms=ops.sm_count(dev()))
-            s = s if s in splits else 1
-            whole = ops.grouped_gemm(x, packed, descs[splits.index(s)], s, [t], n_out)
-            assert torch.equal(y[:32], whole[:32])       # rows of the fp16 form do not depend on their batch
-            assert oracle.rel_err(y[32:].float().cpu().numpy(), whole[32:].float().cpu().numpy()) < TOL_TIGHT
+def test_row_count_dispatch_takes_the_tcgen05_path_from_33_rows():
+    """Up to 32 rows the op runs the grouped kernel, from 33 rows the tcgen05 kernel: same tolerance on both sides of the
+    boundary, and bit-identical to calling the kernel of that side directly — for a run wide enough to fill the GPU and
+    for a narrow one (where the tcgen05 kernel splits K)."""
+    for n_out, k in ((64 * 2 * ops.sm_count(dev()), 512), (320, 5120)):
+        t = F.Q4_K
+        raw = synth.random_blocks(n_out, k, t, seed=77)
+        tl = ops.repack_tiles(raw.to(dev()), n_out, t)
+        packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer([tl], [n_out], [t])
+        d1 = descs[splits.index(1)]
+        for m in (32, 33, 64, 65):
+            x = synth.activations(m, k, device=dev())
+            y = ops.fused_mul_mat_gguf_tiles_grouped(x, packed, descs, splits, views, [n_out], [t], nb, bb)
+            assert oracle.rel_err(y.float().cpu().numpy(), ref_gemm(x, raw, t)) < TOL_TIGHT
+            if m > ops.DECODE_MAX_ROWS:
+                assert torch.equal(y, ops.prefill_gemm(x, packed, d1, n_out, wtypes=[t]))
+            else:
+                s = ops.grouped_split_for(n_out // 64, nb, m=m, block_bytes=bb, sms=ops.sm_count(dev()))
+                s = s if s in splits else 1
+                assert torch.equal(y, ops.grouped_gemm(x, packed, descs[splits.index(s)], s, [t], n_out))
 
 
 def test_prefill_full_size_down_projection_properties():

@@ -194,7 +194,7 @@ def test_arithmetic_error_beyond_the_output_rounding(t):
     tiles = ops.repack_tiles(raw.to(dev()), n_out, t)
     packed, views, descs, splits, nb, bb = ops.prepare_grouped_layer([tiles], [n_out], [t])
     w = oracle.dequantize(raw.numpy(), t).astype(np.float64)
-    for m, form in ((1, "integer"), (8, "integer"), (16, "integer"), (32, "fp16"), (64, "fp16"), (128, "tcgen05")):
+    for m, form in ((1, "integer"), (8, "integer"), (16, "integer"), (17, "fp16"), (32, "fp16"), (64, "tcgen05"), (128, "tcgen05")):
         x = synth.activations(m, k, device=dev())
         y = ops.fused_mul_mat_gguf_tiles_grouped(x, packed, descs, splits, views, [n_out], [t], nb, bb).float().cpu().numpy().astype(np.float64)
         xf = x.float().cpu().numpy().astype(np.float64)
