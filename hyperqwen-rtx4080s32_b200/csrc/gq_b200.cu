@@ -668,12 +668,12 @@ __device__ __forceinline__ void slab_kblock8(const uint8_t *slab, const uint8_t 
     dec.load(slab, lane, aux);
     const int g = lane >> 2, t = lane & 3;
     const uint8_t *xb = xs + g * GQ_X8_ROW + 16 * t;     // unit (i, t) of batch row g; + 8 nt rows, + 256 for the low plane
-    int aH[MT][4], aL[MT][4];
+    int aH[MT][4], aL[MT][4], bH[MT][4], bL[MT][4];
     float bf[MT][4];
 #pragma unroll
     for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { aH[nt][j] = 0; aL[nt][j] = 0; bf[nt][j] = 0.f; }
+        for (int j = 0; j < 4; ++j) { aH[nt][j] = 0; aL[nt][j] = 0; bH[nt][j] = 0; bL[nt][j] = 0; bf[nt][j] = 0.f; }
     static_for<0, 4>([&](auto i_) {
         constexpr int I = decltype(i_)::value;
         uint4 xh[MT], xl[MT];
@@ -712,8 +712,14 @@ __device__ __forceinline__ void slab_kblock8(const uint8_t *slab, const uint8_t 
                     const uint32_t bh0 = V ? xh[nt].z : xh[nt].x, bh1 = V ? xh[nt].w : xh[nt].y;
                     const uint32_t bl0 = V ? xl[nt].z : xl[nt].x, bl1 = V ? xl[nt].w : xl[nt].y;
                     if constexpr (D::SCHEME == GQ_FOLD) {
-                        imma32<AS, true>(aH[nt], a, bh0, bh1, aH[nt][0], aH[nt][1], aH[nt][2], aH[nt][3]);
-                        imma32<AS, false>(aL[nt], a, bl0, bl1, aL[nt][0], aL[nt][1], aL[nt][2], aL[nt][3]);
+                        // two accumulator chains per plane (even / odd k-steps): half the dependent MMAs in a row
+                        if constexpr (V == 0) {
+                            imma32<AS, true>(aH[nt], a, bh0, bh1, aH[nt][0], aH[nt][1], aH[nt][2], aH[nt][3]);
+                            imma32<AS, false>(aL[nt], a, bl0, bl1, aL[nt][0], aL[nt][1], aL[nt][2], aL[nt][3]);
+                        } else {
+                            imma32<AS, true>(bH[nt], a, bh0, bh1, bH[nt][0], bH[nt][1], bH[nt][2], bH[nt][3]);
+                            imma32<AS, false>(bL[nt], a, bl0, bl1, bL[nt][0], bL[nt][1], bL[nt][2], bL[nt][3]);
+                        }
                     } else {
                         int th[4], tl[4];
                         imma32<AS, true>(th, a, bh0, bh1, 0, 0, 0, 0);
@@ -749,7 +755,7 @@ __device__ __forceinline__ void slab_kblock8(const uint8_t *slab, const uint8_t 
             for (int j = 0; j < 4; ++j) tot[j] = bf[nt][j];
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) tot[j] = (j < 2 ? d0 : d1) * fmaf((float)aH[nt][j], 256.0f, (float)aL[nt][j]);
+            for (int j = 0; j < 4; ++j) tot[j] = (j < 2 ? d0 : d1) * fmaf((float)(aH[nt][j] + bH[nt][j]), 256.0f, (float)(aL[nt][j] + bL[nt][j]));
         }
         if constexpr (D::NCORR > 0) {
             const uint8_t *sb = xs + (nt * 8 + g) * GQ_X8_ROW + GQ_X8_SUMS + 8 * t;
