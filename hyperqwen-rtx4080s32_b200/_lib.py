@@ -36,6 +36,8 @@ SIGNATURES = {
     "gq_gemv_grouped": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _vp]),
     "gq_gemv_grouped_phases": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _vp, _i32]),
     "gq_gemv_grouped_prefetch": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _vp, _vp, _i64]),
+    "gq_gemv_grouped_pre": (_i32, [_vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _i64, ctypes.c_float, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp,
+                                   _i64, _vp]),
     "gq_static_workspace_limit": (_i64, []),
     "gq_gemv_grouped_static": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp]),
     "gq_allreduce_buffer_bytes": (_i64, [_i32, _i64]),

@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(256) unrepack_kernel(int type, int B, const ui
 // explicit round-to-nearest multiplies and subtracts so nothing is fused)
 // ---------------------------------------------------------------------------------------------------
 __constant__ uint32_t c_iq3s_grid[512];
+__constant__ uint32_t c_iq3xxs_grid[256];
 __constant__ int8_t c_iq4_kvalues[16];
 
 // A bounded wait that runs out is reported twice: in the status word of the launch's workspace (gq_read_status) and in
@@ -178,6 +179,12 @@ __device__ float deq_one(int type, const uint8_t *b, int w) {
             const int idx = b[2 + 8 * ib + k] | (((b[66 + ib] >> k) & 1) << 8);
             const float mag = (float)((c_iq3s_grid[idx] >> (8 * e)) & 0xFF);
             const float v = __fmul_rn(db, mag); return ((b[74 + 4 * ib + (j >> 3)] >> (j & 7)) & 1) ? -v : v; }
+        case GQ_IQ3_XXS: { const int ib = w >> 5, j = w & 31; const uint8_t *q = b + 66 + 4 * ib;
+            const uint32_t sw = q[0] | (q[1] << 8) | (q[2] << 16) | ((uint32_t)q[3] << 24);
+            const float db = __fmul_rn(__fmul_rn(h2f(b), 0.5f + (float)(sw >> 28)), 0.5f);
+            const uint32_t f = (sw >> (7 * (j >> 3))) & 0x7Fu, mask = f | (((uint32_t)__popc(f) & 1u) << 7);
+            const float mag = (float)((c_iq3xxs_grid[b[2 + 8 * ib + (j >> 2)]] >> (8 * (j & 3))) & 0xFF);
+            const float v = __fmul_rn(db, mag); return ((mask >> (j & 7)) & 1) ? -v : v; }
         case GQ_IQ4_XS: { const int ib = w >> 5, j = w & 31; const uint32_t sh = b[2] | (b[3] << 8);
             const int ls = (int)(((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
             const float dl = __fmul_rn(h2f(b), (float)ls);
@@ -233,6 +240,9 @@ __host__ __device__ inline int64_t align256(int64_t v) { return (v + 255) & ~(in
 // reads them: 16-byte unit 4*i + t holds, for runs 4i..4i+3, the quad 4t..4t+3 with bytes in the order (0,2,1,3).
 // 576 = 64 mod 128, so the two rows a quarter-warp reads with one 16-byte load each sit in different banks.
 // After the rows of a k-block come their scales 2^-e (fp32, one per batch row, padded to a multiple of 16 bytes).
+#define GQ_PRE_NONE 0
+#define GQ_PRE_SILU_MUL 1
+#define GQ_PRE_ADD_RMSNORM 2
 #define GQ_X8_ROW 576
 #define GQ_X8_SUMS 512
 #ifndef GQ_GEMV8_MAX_ROWS
@@ -365,10 +375,6 @@ __global__ void __launch_bounds__(GQ_PREP_THREADS) prep_x_kernel(const __nv_bflo
 }
 
 
-#ifdef GQ_TRACE
-__device__ unsigned long long g_ptl[64 * 4];
-extern "C" int gq_prep_timeline_read(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, g_ptl, sizeof g_ptl); }
-#endif
 // ---------------------------------------------------------------------------------------------------
 // activation preparation, integer form (1..16 batch rows): one warp per (batch row, k-block).  The 256 activations
 // become 16-bit fixed point at a power-of-two scale of their own (exact for every value within 2^-7 of the block's
@@ -378,31 +384,39 @@ extern "C" int gq_prep_timeline_read(unsigned long long *host) { return (int)cud
 // ---------------------------------------------------------------------------------------------------
 #define GQ_PREP8_WARPS 8
 
-__global__ void __launch_bounds__(32 * GQ_PREP8_WARPS) prep_x8_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int M, uint8_t *__restrict__ xt,
-                                                                      int *status) {
-    const int lane = threadIdx.x & 31, kb = blockIdx.x;
-    const int m = blockIdx.y * GQ_PREP8_WARPS + (threadIdx.x >> 5);
-#ifdef GQ_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 64) g_ptl[blockIdx.x * 4 + 0] = global_timer_ns();
-#endif
-    pdl_trigger();    // the grouped kernel behind this one may start fetching weights
-    pdl_wait();       // whatever ran before (possibly still reading this workspace) has finished
-#ifdef GQ_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 64) g_ptl[blockIdx.x * 4 + 1] = global_timer_ns();
-#endif
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *status = 0;
-    if (m >= M) return;
-    const __nv_bfloat16 *xr = x + (int64_t)m * ldx + (int64_t)kb * GQ_QK + 8 * lane;
-    float v[8];
-    if ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xr));
+// The op in front of a linear layer, folded into its activation preparation: what vLLM runs as a kernel of its own
+// between two linears reads its input here, on the way into the fixed-point planes, instead of writing a bf16 tensor
+// that the preparation reads back.  The arithmetic repeats the unfused kernels' (bf16 wherever they round to bf16).
+//   GQ_PRE_SILU_MUL     x = silu(gate) * up with gate = in[:, :K], up = in[:, K:2K]: vLLM's silu_and_mul in front of
+//                       down_proj
+//   GQ_PRE_ADD_RMSNORM  z = in + residual (stored to residual_out), x = z * rsqrt(mean(z^2) + eps) * weight: vLLM's
+//                       fused_add_rms_norm in front of qkv_proj / gate_up_proj; without a residual, plain RMSNorm
+// (The reference serves the model with the unfused ops of stock vLLM; its own fusion is the kernel's batching of
+// shards, gguf-plugin/gluon/tiles_grouped.py:1204-1313.)
+struct PreOp {
+    int kind, K;
+    const __nv_bfloat16 *weight;          // [K]
+    const __nv_bfloat16 *residual;        // [M, ld_res] or null
+    __nv_bfloat16 *residual_out;          // [M, ld_res], written when residual is given; never the same memory
+    int64_t ld_res;
+    float eps;
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p));
         const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&raw);
 #pragma unroll
         for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
     } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(xr[j]);
+        for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(p[j]);
     }
+}
+__device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+
+// one warp: the 256 activations of batch row m, k-block kb (8 per lane, consecutive) -> planes, run sums, scale
+__device__ __forceinline__ void prep8_store(const float (&v)[8], int kb, int m, int M, uint8_t *__restrict__ xt, int lane) {
     float amax = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
@@ -444,9 +458,90 @@ __global__ void __launch_bounds__(32 * GQ_PREP8_WARPS) prep_x8_kernel(const __nv
         so[16 + r] = lo;
     }
     if (lane == 0) *reinterpret_cast<float *>(xt + (int64_t)kb * gq_x8_tile_bytes(M) + (int64_t)M * GQ_X8_ROW + 4 * m) = inv;
-#ifdef GQ_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 64) g_ptl[blockIdx.x * 4 + 2] = global_timer_ns();
-#endif
+}
+
+
+template <int PRE>
+__global__ void __launch_bounds__(32 * GQ_PREP8_WARPS) prep_x8_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int M, uint8_t *__restrict__ xt,
+                                                                      int *status, const PreOp pre) {
+    const int lane = threadIdx.x & 31, kb = blockIdx.x;
+    const int m = blockIdx.y * GQ_PREP8_WARPS + (threadIdx.x >> 5);
+    pdl_trigger();    // the grouped kernel behind this one may start fetching weights
+    pdl_wait();       // whatever ran before (possibly still reading this workspace) has finished
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *status = 0;
+    if (m >= M) return;
+    const __nv_bfloat16 *xr = x + (int64_t)m * ldx + (int64_t)kb * GQ_QK + 8 * lane;
+    float v[8];
+    load8(xr, v);
+    if constexpr (PRE == GQ_PRE_SILU_MUL) {
+        float u[8];
+        load8(xr + pre.K, u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = bf16_round(bf16_round(v[j] / (1.0f + expf(-v[j]))) * u[j]);
+    }
+    prep8_store(v, kb, m, M, xt, lane);
+}
+
+// RMSNorm (with the residual add) in front of the layer: grid (batch rows, k-blocks / 8).  Every CTA sums the squares of
+// its whole row (a few KB from L2), then each warp converts one k-block.
+__global__ void __launch_bounds__(32 * GQ_PREP8_WARPS) prep_x8_norm_kernel(const __nv_bfloat16 *__restrict__ x, int64_t ldx, int M, uint8_t *__restrict__ xt,
+                                                                           int *status, const PreOp pre) {
+    __shared__ float red[GQ_PREP8_WARPS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, m = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *status = 0;
+    const __nv_bfloat16 *row = x + (int64_t)m * ldx;
+    const __nv_bfloat16 *res = pre.residual ? pre.residual + (int64_t)m * pre.ld_res : nullptr;
+    float ss = 0.0f;
+#pragma unroll 4
+    for (int c = threadIdx.x; c < pre.K / 8; c += 32 * GQ_PREP8_WARPS) {
+        float a[8];
+        load8(row + 8 * c, a);
+        if (res) {
+            float r[8];
+            load8(res + 8 * c, r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] = bf16_round(a[j] + r[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(a[j], a[j], ss);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < GQ_PREP8_WARPS; ++i) ss += red[i];
+    const float rs = rsqrtf(ss / (float)pre.K + pre.eps);
+    const int kb = blockIdx.y * GQ_PREP8_WARPS + warp;
+    if (kb < pre.K / GQ_QK) {
+        const int64_t col = (int64_t)kb * GQ_QK + 8 * lane;
+        float v[8], w[8];
+        load8(row + col, v);
+        load8(pre.weight + col, w);
+        if (res) {
+            float r[8];
+            load8(res + col, r);
+            uint4 z;
+            __nv_bfloat162 *zb = reinterpret_cast<__nv_bfloat162 *>(&z);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = bf16_round(v[j] + r[j]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) zb[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            __nv_bfloat16 *zo = pre.residual_out + (int64_t)m * pre.ld_res + col;
+            if ((reinterpret_cast<uintptr_t>(zo) & 15) == 0) {
+                *reinterpret_cast<uint4 *>(zo) = z;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) zo[j] = __float2bfloat16_rn(v[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = bf16_round(bf16_round(v[j] * rs) * w[j]);
+        prep8_store(v, kb, m, M, xt, lane);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -576,15 +671,6 @@ __device__ __forceinline__ void slab_kblock(const uint8_t *slab, const uint8_t *
     }
 }
 
-#ifdef GQ_TRACE
-__device__ long long g_trace[1024 * 64 * 4];
-__device__ unsigned long long g_tl[1024 * 8];    // per CTA wall-clock marks (ns): entry, prologue end, pdl wait end, first data, loop end, exit
-extern "C" int gq_trace_read(long long *host) { return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof g_trace); }
-extern "C" int gq_timeline_read(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, g_tl, sizeof g_tl); }
-#define GQ_MARK(k) do { if (blockIdx.x < 1024) g_tl[blockIdx.x * 8 + (k)] = global_timer_ns(); } while (0)
-#else
-#define GQ_MARK(k) do { } while (0)
-#endif
 
 // The stage ring of one CTA: per stage the weight tile of one k-block and the matching activation tile, filled by two
 // bulk copies that complete on the stage's "full" mbarrier; the four consumer warps hand a stage back through its
@@ -779,24 +865,11 @@ __device__ __forceinline__ void slab_kblock8(const uint8_t *slab, const uint8_t 
 template <int TYPE, int MT>
 __device__ __forceinline__ bool consume8(const Ring &r, int xs_off, int slab_off, const DecAux8 &aux, int lane, float (&acc)[MT][4]) {
     for (int i = 0, s = 0, round = 0; i < r.nk; ++i) {
-#ifdef GQ_TRACE
-        const long long ta = clock64();
-#endif
         if (!mbar_wait(r.full + s, round & 1)) return false;
-#ifdef GQ_TRACE
-        const long long tb = clock64();
-        if (i == 0 && lane == 0 && slab_off == 0) GQ_MARK(3);
-#endif
         const uint8_t *st = r.smem + (size_t)s * r.stage_bytes;
         slab_kblock8<TYPE, MT>(st + slab_off, st + r.wmax, xs_off, aux, lane, acc);
         __syncwarp();
         if (lane == 0) mbar_arrive(r.empty + s);
-#ifdef GQ_TRACE
-        if (lane == 0 && slab_off == 0 && blockIdx.x < 1024 && i < 64) {
-            long long *t = g_trace + ((size_t)blockIdx.x * 64 + i) * 4;
-            t[0] = ta; t[1] = tb; t[2] = clock64();
-        }
-#endif
         if (++s == r.stages) { s = 0; ++round; }
     }
     return true;
@@ -895,7 +968,6 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     uint2 *grid_s = reinterpret_cast<uint2 *>(empty + stages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) GQ_MARK(0);
     const int32_t *d = p.desc + (int64_t)blockIdx.x * GQ_DESC_WORDS;
     const int64_t off = (int64_t)d[0] * 16;
     const int type = ONLY ? ONLY : d[1];
@@ -916,13 +988,20 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         if constexpr (FORM) { for (int i = threadIdx.x; i < 512; i += blockDim.x) reinterpret_cast<uint32_t *>(grid_s)[i] = iq3s_grid_entry8(c_iq3s_grid[i]); }
         else { for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]); }
     }
+    if ((ONLY == 0 || ONLY == GQ_IQ3_XXS) && p.has_iq3s && type == GQ_IQ3_XXS) {
+        if constexpr (FORM) {
+            uint32_t *g8 = reinterpret_cast<uint32_t *>(grid_s);
+            for (int i = threadIdx.x; i < 256; i += blockDim.x) { g8[i] = iq3s_grid_entry8(c_iq3xxs_grid[i]); g8[256 + i] = iq3xxs_sign_entry8((uint32_t)i); }
+        } else {
+            for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_s[GQ_IQ3XXS_GRID_OFFSET + i] = iq3s_grid_entry(c_iq3xxs_grid[i]);
+        }
+    }
     __syncthreads();
     // push-form split-K: a CTA may store into the split-0 CTA's shared memory only once that CTA is known to run;
     // every thread enters this rendezvous here and collects it just before its first remote store (or before the
     // closing barrier), long after everyone has arrived
     const bool push = p.cluster && p.cluster_push;
     if (push) cluster_arrive_relaxed();
-    if (threadIdx.x == 0) GQ_MARK(1);
 
     if (warp == GQ_CONSUMER_WARPS) {
         // ---- producer: one thread; per k-block one bulk copy of the weight tile and one of the activation tile.
@@ -939,7 +1018,6 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
                 bulk_g2s(smem + (size_t)i * stage_bytes, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + i);
             }
             pdl_wait();
-            GQ_MARK(2);
             for (int i = 0; i < pre; ++i) bulk_g2s(smem + (size_t)i * stage_bytes + wmax, xsrc + (int64_t)i * abytes, abytes, full + i);
             if (nk - pre <= 2) pdl_trigger();
             for (int i = pre, s = 0, round = 1; i < nk; ++i) {
@@ -948,9 +1026,6 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
                 mbar_expect_tx(full + s, (uint32_t)tile_bytes + abytes);
                 bulk_g2s(st, src + (int64_t)i * tile_bytes, (uint32_t)tile_bytes, full + s);
                 bulk_g2s(st + wmax, xsrc + (int64_t)i * abytes, abytes, full + s);
-#ifdef GQ_TRACE
-                if (blockIdx.x < 1024 && i < 64) g_trace[((size_t)blockIdx.x * 64 + i) * 4 + 3] = clock64();
-#endif
                 if (i == nk - 3) pdl_trigger();
                 if (++s == stages) { s = 0; ++round; }
             }
@@ -993,7 +1068,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     }
     if constexpr (FORM) {
         DecAux8 aux;
-        aux.iq3s_grid = reinterpret_cast<const uint32_t *>(grid_s);
+        aux.grid = reinterpret_cast<const uint32_t *>(grid_s);
         aux.iq4 = iq4;
         const int xs_off = M * GQ_X8_ROW;
 #define GQ_CONSUME(T) case T: ok = consume8<T, MT>(ring, xs_off, slab_off, aux, lane, acc); break;
@@ -1002,23 +1077,22 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         } else {
             switch (type) {
                 GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
-                GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS)
+                GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS) GQ_CONSUME(GQ_IQ3_XXS)
             }
         }
 #undef GQ_CONSUME
     } else {
         DecAux aux;
-        aux.iq3s_grid = grid_s;
+        aux.grid = grid_s;
         aux.iq4 = iq4;
 #define GQ_CONSUME(T) case T: ok = consume<T, MT>(ring, slab_off, aux, lane, acc); break;
         switch (type) {
             GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
-            GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS)
+            GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS) GQ_CONSUME(GQ_IQ3_XXS)
         }
 #undef GQ_CONSUME
     }
     if (!ok && lane == 0) report_status(p.status, GQ_DEV_TIMEOUT);   // the result is then incomplete; the status word says so
-    if (threadIdx.x == 0) GQ_MARK(4);
 
     // ---- epilogue: rows of the MMA are output columns, columns of the MMA are batch rows ----
     const int g = lane >> 2, t = lane & 3;
@@ -1100,7 +1174,6 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
                 else p.partials[((int64_t)split_idx * p.M + n) * p.n_total + col0 + r] = v;
             }
         }
-    if (threadIdx.x == 0) GQ_MARK(5);
 }
 
 // Y = sum over splits of the fp32 partials, rounded once to bf16 (reference: sum_partials,
@@ -1125,6 +1198,7 @@ static int ensure_tables() {
     GQ_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && (done_mask.load() >> dev) & 1ull) return GQ_OK;
     GQ_CUDA(cudaMemcpyToSymbol(c_iq3s_grid, GQ_IQ3S_GRID, sizeof GQ_IQ3S_GRID));
+    GQ_CUDA(cudaMemcpyToSymbol(c_iq3xxs_grid, GQ_IQ3XXS_GRID, sizeof GQ_IQ3XXS_GRID));
     GQ_CUDA(cudaMemcpyToSymbol(c_iq4_kvalues, GQ_IQ4_KVALUES, sizeof GQ_IQ4_KVALUES));
     if (dev < 64) done_mask.fetch_or(1ull << dev);
     return GQ_OK;
@@ -1281,7 +1355,7 @@ static int launch_gemv8_m8(const GemvParams &p, int64_t n_desc, cudaStream_t st,
     switch (only) {
 #define GQ_ONE(T) case T: return launch_gemv<1, 4, 1, T>(p, n_desc, st);
         GQ_ONE(GQ_Q4_0) GQ_ONE(GQ_Q5_0) GQ_ONE(GQ_Q8_0) GQ_ONE(GQ_Q2_K) GQ_ONE(GQ_Q3_K) GQ_ONE(GQ_Q4_K)
-        GQ_ONE(GQ_Q5_K) GQ_ONE(GQ_Q6_K) GQ_ONE(GQ_IQ4_NL) GQ_ONE(GQ_IQ3_S) GQ_ONE(GQ_IQ4_XS)
+        GQ_ONE(GQ_Q5_K) GQ_ONE(GQ_Q6_K) GQ_ONE(GQ_IQ4_NL) GQ_ONE(GQ_IQ3_S) GQ_ONE(GQ_IQ4_XS) GQ_ONE(GQ_IQ3_XXS)
 #undef GQ_ONE
         default: return launch_gemv<1, 4, 1, 0>(p, n_desc, st);
     }
@@ -1294,7 +1368,7 @@ extern "C" int gq_run_info(int n_shards, const int32_t *types) {
         const int B = gq_type_bytes(types[i]);
         if (!B) return GQ_ERR_TYPE;
         if (B > maxb) maxb = B;
-        if (types[i] == GQ_IQ3_S) iq3s = 1;
+        if (types[i] == GQ_IQ3_S || types[i] == GQ_IQ3_XXS) iq3s = 1;      // a codebook type: the kernels keep its grid in shared memory
         if (types[i] != single) single = 0;
     }
     return maxb | (iq3s << 16) | (single << 17);
@@ -1303,7 +1377,7 @@ extern "C" int gq_run_info(int n_shards, const int32_t *types) {
 static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
                              int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total, void *workspace_dev,
                              int64_t workspace_bytes, void *stream, int phases, const void *next_packed_dev, int64_t next_bytes,
-                             const ArFused *ar = nullptr) {
+                             const ArFused *ar = nullptr, const PreOp *pre = nullptr) {
     if (M < 0 || M > GQ_MAX_GEMV_ROWS || K <= 0 || K % GQ_QK || n_total < 0 || n_desc < 0 || split < 1) return GQ_ERR_SHAPE;
     if (M == 0 || n_total == 0 || n_desc == 0) return GQ_OK;
     if (!x_dev || !packed_dev || !desc_dev || !y_dev || !workspace_dev) return GQ_ERR_ARG;
@@ -1324,8 +1398,16 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         cfg.dynamicSmemBytes = 0; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
         if (form) {
             cfg.gridDim = dim3((unsigned)(K / GQ_QK), (unsigned)((M + GQ_PREP8_WARPS - 1) / GQ_PREP8_WARPS)); cfg.blockDim = dim3(32 * GQ_PREP8_WARPS);
-            GQ_CUDA(cudaLaunchKernelEx(&cfg, prep_x8_kernel, (const __nv_bfloat16 *)x_dev, ldx, (int)M, ws.xt, ws.status));
+            const PreOp po = pre ? *pre : PreOp{};
+            if (po.kind == GQ_PRE_ADD_RMSNORM) {
+                cfg.gridDim = dim3((unsigned)M, (unsigned)((K / GQ_QK + GQ_PREP8_WARPS - 1) / GQ_PREP8_WARPS));
+                GQ_CUDA(cudaLaunchKernelEx(&cfg, prep_x8_norm_kernel, (const __nv_bfloat16 *)x_dev, ldx, (int)M, ws.xt, ws.status, po));
+            } else {
+                auto *kern = po.kind == GQ_PRE_SILU_MUL ? prep_x8_kernel<GQ_PRE_SILU_MUL> : prep_x8_kernel<GQ_PRE_NONE>;
+                GQ_CUDA(cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16 *)x_dev, ldx, (int)M, ws.xt, ws.status, po));
+            }
         } else {
+            if (pre && pre->kind) return GQ_ERR_SHAPE;      // the folded ops exist in the integer form's preparation only
             cfg.gridDim = dim3((unsigned)M); cfg.blockDim = dim3(GQ_PREP_THREADS);
             GQ_CUDA(cudaLaunchKernelEx(&cfg, prep_x_kernel, (const __nv_bfloat16 *)x_dev, ldx, (int)K, (int)M, ws.ex, ws.xt, ws.status));
         }
@@ -1410,6 +1492,32 @@ extern "C" int gq_gemv_grouped(const void *x_dev, int64_t M, int64_t K, int64_t 
                                int64_t workspace_bytes, void *stream) {
     return gq_gemv_grouped_phases(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
                                   workspace_bytes, stream, 7);
+}
+
+// ---- the same call with the op in front of the layer folded into the activation preparation -----------------
+// pre_op GQ_PRE_SILU_MUL: x_dev is the [M, 2K] output of gate_up_proj (ldx >= 2K), the layer multiplies
+// silu(x[:, :K]) * x[:, K:].  GQ_PRE_ADD_RMSNORM: x_dev is [M, K]; norm_weight [K]; residual_in / residual_out [M, ld_res]
+// both or neither (distinct memory: every warp of a row reads the whole old residual).  1..GQ_GEMV8_MAX_ROWS rows.
+extern "C" int gq_gemv_grouped_pre(const void *x_dev, int64_t M, int64_t K, int64_t ldx, int pre_op, const void *norm_weight_dev,
+                                   const void *residual_in_dev, void *residual_out_dev, int64_t ld_res, float eps, const void *packed_dev,
+                                   const int32_t *desc_dev, int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy,
+                                   int64_t n_total, void *workspace_dev, int64_t workspace_bytes, void *stream) {
+    if (M < 0 || M > GQ_GEMV8_MAX_ROWS) return GQ_ERR_SHAPE;
+    PreOp po{};
+    po.kind = pre_op; po.K = (int)K; po.eps = eps;
+    if (pre_op == GQ_PRE_SILU_MUL) {
+        if (ldx < 2 * K) return GQ_ERR_ARG;
+    } else if (pre_op == GQ_PRE_ADD_RMSNORM) {
+        if (!norm_weight_dev || ((uintptr_t)norm_weight_dev & 1)) return GQ_ERR_ARG;
+        if ((residual_in_dev == nullptr) != (residual_out_dev == nullptr)) return GQ_ERR_ARG;
+        if (residual_in_dev && (residual_in_dev == residual_out_dev || ld_res < K)) return GQ_ERR_ARG;
+        po.weight = (const __nv_bfloat16 *)norm_weight_dev;
+        po.residual = (const __nv_bfloat16 *)residual_in_dev; po.residual_out = (__nv_bfloat16 *)residual_out_dev; po.ld_res = ld_res;
+    } else if (pre_op != GQ_PRE_NONE) {
+        return GQ_ERR_ARG;
+    }
+    return gemv_grouped_impl(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
+                             workspace_bytes, stream, 7, nullptr, 0, nullptr, &po);
 }
 
 // ---- the same call for callers that cannot allocate device memory -------------------------------------

@@ -235,6 +235,24 @@ GQ_HD inline uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
     return h2_as_u32(__floats2half2_rn((float)lo, (float)hi));
 #endif
 }
+// rotate right by n (0..31), and the number of set bits: device instructions with a host restatement
+GQ_HD inline uint32_t rotr32(uint32_t w, int n) {
+#ifdef __CUDA_ARCH__
+    return __funnelshift_r(w, w, n);
+#else
+    n &= 31;
+    return n ? (w >> n) | (w << (32 - n)) : w;
+#endif
+}
+GQ_HD inline uint32_t popc32(uint32_t w) {
+#ifdef __CUDA_ARCH__
+    return (uint32_t)__popc(w);
+#else
+    uint32_t c = 0;
+    for (; w; w &= w - 1) ++c;
+    return c;
+#endif
+}
 // a 16-bit fp16 constant in both halves
 GQ_HD constexpr uint32_t h2c(uint32_t h16) { return h16 | (h16 << 16); }
 

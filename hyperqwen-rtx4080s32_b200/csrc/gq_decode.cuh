@@ -70,7 +70,7 @@ GQ_HD inline void iq4_word(uint32_t w, const Iq4Table &T, uint32_t (&lo)[2], uin
 GQ_HD inline uint32_t bytes_h2(uint32_t w, uint32_t sel) { return prmt(w, GQ_MAGICB, sel); }
 
 struct DecAux {
-    const uint2 *iq3s_grid;   // shared memory: 512 entries, {fp16(m0,m1), fp16(m2,m3)}
+    const uint2 *grid;        // shared memory: the codebook of the CTA's type (IQ3_S 512, IQ3_XXS 256 entries), {fp16(m0,m1), fp16(m2,m3)}
     Iq4Table iq4;
 };
 
@@ -636,7 +636,10 @@ struct Dec<GQ_Q3_K> {
     template <int R> static constexpr float offs() { return float((1024 >> (2 * ((R >> 1) & 3))) + 4); }
 };
 
-#define GQ_IQ3S_SMEM_BYTES 4096
+// fp16 form: the IQ3_S grid (512 x 8 bytes) followed by the IQ3_XXS grid (256 x 8 bytes); a CTA fills the tables of
+// the types it decodes (the tcgen05 kernel's two tiles may differ in type)
+#define GQ_IQ3S_SMEM_BYTES 6144
+#define GQ_IQ3XXS_GRID_OFFSET 512
 // ---- IQ3_S ----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_IQ3_S> {
@@ -648,7 +651,7 @@ struct Dec<GQ_IQ3_S> {
     uint32_t sce[2], sco[2], dd[2];   // scale nibbles of even / odd sub-blocks, one per byte
     const uint2 *grid;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
-        grid = aux.iq3s_grid;
+        grid = aux.grid;
         const int t = lane & 3;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -699,7 +702,63 @@ struct Dec<GQ_IQ3_S> {
 };
 
 
-// one entry of the IQ3_S shared-memory grid: the four magnitude bytes of a grid word as two fp16 pairs
+// ---- IQ3_XXS: d | 64 grid-index bytes | eight words of four 7-bit sign indices and a 4-bit scale ----------------
+// weight = d (2 s + 1) / 4 x magnitude x sign; the eighth sign of a group of eight is the parity of the stored seven
+// (gguf-plugin/gluon/iq3xxs.py:5-19)
+template <>
+struct Dec<GQ_IQ3_XXS> {
+    static constexpr int GROUP = 32;
+    static constexpr int NCORR = 0;
+    uint4 q[2];          // 16 grid-index bytes per row (byte r = run r)
+    uint32_t sw[2][8];   // the sign-and-scale word of each sub-block
+    uint32_t dd[2];
+    int sh0, shn;        // 7 (t >> 1): the lane's sign index inside a half sub-block; 4 (t & 1): its nibble of the mask
+    const uint2 *grid;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
+        grid = aux.grid + GQ_IQ3XXS_GRID_OFFSET;
+        const int t = lane & 3;
+        sh0 = 7 * (t >> 1);
+        shn = 4 * (t & 1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            q[h] = ld16(slab + 512 * h + 16 * lane);
+            const uint4 a = ld16(slab + 1024 + 32 * row), b = ld16(slab + 1040 + 32 * row);
+            sw[h][0] = a.x; sw[h][1] = a.y; sw[h][2] = a.z; sw[h][3] = a.w;
+            sw[h][4] = b.x; sw[h][5] = b.y; sw[h][6] = b.z; sw[h][7] = b.w;
+            dd[h] = ld2(slab + 1536 + 2 * row);
+        }
+    }
+    template <int R>
+    GQ_HD void run(int h, uint32_t &a01, uint32_t &a23) const {
+        const uint32_t idx = (w4(q[h], R >> 2) >> (8 * (R & 3))) & 0xFFu;
+        const uint2 e = grid[idx];
+        const uint32_t f = (sw[h][R >> 1] >> (14 * (R & 1) + sh0)) & 0x7Fu;
+        const uint32_t mask = f | (popc32(f) << 7);          // bit 7: the parity (higher bits fall outside the nibble)
+        const uint32_t nib = (mask >> shn) & 0xFu;
+        a01 = xor_and(e.x, nib * 0x40008000u, 0x80008000u);
+        a23 = xor_and(e.y, (nib >> 2) * 0x40008000u, 0x80008000u);
+    }
+    template <int P>
+    GQ_HD void pair(uint32_t (&a)[2][4]) const {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            run<2 * P>(h, a[0][h], a[0][2 + h]);
+            run<2 * P + 1>(h, a[1][h], a[1][2 + h]);
+        }
+    }
+    // 2 s + 1 dropped into the mantissa of 2^23, minus 2^23
+    template <int G>
+    GQ_HD void scale(float &s0, float &s1) const {
+        s0 = u32_as_f32(0x4B000001u + 2u * (sw[0][G] >> 28)) - 8388608.0f;
+        s1 = u32_as_f32(0x4B000001u + 2u * (sw[1][G] >> 28)) - 8388608.0f;
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.25f * f16bits(dd[0]); d1 = 0.25f * f16bits(dd[1]); }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 0.0f; }
+};
+
+// one entry of the IQ3_S / IQ3_XXS shared-memory grid: the four magnitude bytes of a grid word as two fp16 pairs
 GQ_HD inline uint2 iq3s_grid_entry(uint32_t w) {
     uint2 e;
     e.x = h2_as_u32(__floats2half2_rn((float)(w & 0xFF), (float)((w >> 8) & 0xFF)));

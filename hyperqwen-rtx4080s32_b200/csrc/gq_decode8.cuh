@@ -27,7 +27,8 @@ namespace gq {
 enum { GQ_S32 = 0, GQ_F32 = 1, GQ_S16 = 2, GQ_FOLD = 3 };
 
 struct DecAux8 {
-    const uint32_t *iq3s_grid;   // shared memory: 512 entries, four magnitude bytes in quad byte order
+    const uint32_t *grid;        // shared memory: the codebook of the CTA's type, four magnitude bytes per entry in quad byte order
+                                 // (IQ3_S 512 entries; IQ3_XXS 256 entries followed by the 128 x 2 sign words)
     Iq4Table iq4;                // the IQ4 codebook as signed bytes
 };
 
@@ -480,7 +481,7 @@ struct Dec8<GQ_IQ3_S> {
     uint32_t sce[2], sco[2], dd[2];   // 1 + 2 s of the even / odd sub-blocks, one per byte
     const uint32_t *grid;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
-        grid = aux.iq3s_grid;
+        grid = aux.grid;
         const int t = lane & 3;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -519,6 +520,62 @@ struct Dec8<GQ_IQ3_S> {
         s1 = ubyte<(S >> 1)>((S & 1) ? sco[1] : sce[1]);
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = f16bits(dd[0]); d1 = f16bits(dd[1]); }
+};
+
+// ---- IQ3_XXS ---------------------------------------------------------------------------------------
+// Shared memory: 256 grid words, then 128 x 2 sign words: entry 2 f + n = spread_sign of nibble n of the 8-bit mask of
+// sign index f (the index with its parity as bit 7).
+#define GQ_IQ3XXS8_SMEM_BYTES 2048
+GQ_HD inline uint32_t iq3xxs_sign_entry8(uint32_t i) {
+    const uint32_t f = i >> 1, mask = f | ((popc32(f) & 1u) << 7);
+    return spread_sign((mask >> (4 * (i & 1))) & 0xFu);
+}
+
+template <>
+struct Dec8<GQ_IQ3_XXS> {
+    static constexpr int SCHEME = GQ_S32;
+    static constexpr bool A_SIGNED = true;
+    static constexpr int NCORR = 0;
+    uint4 q[2];          // 16 grid-index bytes per row (byte r = run r)
+    uint32_t sw[2][8];   // the sign-and-scale word of each sub-block
+    uint32_t dd[2];
+    int rot0, rot1;      // rotate counts that bring the lane's sign index of the first / second run of a sub-block to bits 3..9
+    const uint32_t *grid;
+    const uint8_t *signs;   // the sign words, offset by the lane's nibble
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
+        grid = aux.grid;
+        const int t = lane & 3;
+        signs = reinterpret_cast<const uint8_t *>(aux.grid + 256) + 4 * (t & 1);
+        rot0 = (7 * (t >> 1) - 3) & 31;
+        rot1 = 7 * (2 + (t >> 1)) - 3;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            q[h] = ld16(slab + 512 * h + 16 * lane);
+            const uint4 a = ld16(slab + 1024 + 32 * row), b = ld16(slab + 1040 + 32 * row);
+            sw[h][0] = a.x; sw[h][1] = a.y; sw[h][2] = a.z; sw[h][3] = a.w;
+            sw[h][4] = b.x; sw[h][5] = b.y; sw[h][6] = b.z; sw[h][7] = b.w;
+            dd[h] = ld2(slab + 1536 + 2 * row);
+        }
+    }
+    template <int R, int H>
+    GQ_HD uint32_t quad() const {
+        const uint32_t e = grid[(uint32_t)ubyte<(R & 3)>(w4(q[H], R >> 2))];
+        const uint32_t w = sw[H][R >> 1];
+        const uint32_t off = rotr32(w, (R & 1) ? rot1 : rot0) & 0x3F8u;      // 8 x sign index
+        const uint32_t one = *reinterpret_cast<const uint32_t *>(signs + off);
+        return (e ^ (one * 0xFFu)) + one;       // negated bytes where the sign bit is set
+    }
+    template <int S>
+    GQ_HD void step(uint32_t (&a)[4]) const {
+        a[0] = quad<2 * S, 0>(); a[1] = quad<2 * S, 1>(); a[2] = quad<2 * S + 1, 0>(); a[3] = quad<2 * S + 1, 1>();
+    }
+    template <int S>
+    GQ_HD void iscale(int &s0, int &s1) const {
+        s0 = (int)(2u * (sw[0][S] >> 28) + 1u);
+        s1 = (int)(2u * (sw[1][S] >> 28) + 1u);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.25f * f16bits(dd[0]); d1 = 0.25f * f16bits(dd[1]); }
 };
 
 }  // namespace gq

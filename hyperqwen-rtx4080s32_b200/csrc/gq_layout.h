@@ -22,7 +22,7 @@
 
 enum GqType {
     GQ_Q4_0 = 2, GQ_Q5_0 = 6, GQ_Q8_0 = 8, GQ_Q2_K = 10, GQ_Q3_K = 11, GQ_Q4_K = 12, GQ_Q5_K = 13,
-    GQ_Q6_K = 14, GQ_IQ4_NL = 20, GQ_IQ3_S = 21, GQ_IQ4_XS = 23
+    GQ_Q6_K = 14, GQ_IQ3_XXS = 18, GQ_IQ4_NL = 20, GQ_IQ3_S = 21, GQ_IQ4_XS = 23
 };
 
 #ifdef __CUDACC__
@@ -45,6 +45,7 @@ GQ_HD inline int gq_type_bytes(int type) {
         case GQ_IQ4_NL: return 144;
         case GQ_IQ3_S: return 110;
         case GQ_IQ4_XS: return 136;
+        case GQ_IQ3_XXS: return 98;
         default: return 0;
     }
 }
@@ -58,7 +59,7 @@ GQ_HD inline int gq_type_chunks(int type) {
         case GQ_Q8_0: return 8;
         case GQ_Q2_K: return 2;
         case GQ_Q3_K: return 3;
-        case GQ_IQ3_S: return 2;
+        case GQ_IQ3_S: case GQ_IQ3_XXS: return 2;
         default: return 0;
     }
 }
@@ -104,7 +105,7 @@ GQ_HD inline int gq_slab_src(int type, int p, int *row, int *byte) {
                 *row = g + 8 * h;
                 *byte = c < 2 ? 32 + 32 * c + 16 * u + 4 * t + im : 16 * u + 4 * t + im;
                 return 0;
-            case GQ_IQ3_S: {
+            case GQ_IQ3_S: case GQ_IQ3_XXS: {
                 const int r = 4 * e + z;          // run 0..15: one grid-index byte per run
                 *row = g + 8 * c; *byte = 2 + 8 * (r >> 1) + 4 * (r & 1) + t; return 0;
             }
@@ -146,6 +147,10 @@ GQ_HD inline int gq_slab_src(int type, int p, int *row, int *byte) {
             q -= 128;
             if (q < 64) { *row = q >> 2; *byte = 106 + (q & 3); return 0; }
             q -= 64;
+            *row = q >> 1; *byte = q & 1; return 0;
+        case GQ_IQ3_XXS:                           // the eight sign-and-scale words per row (32 B), then d per row
+            if (q < 512) { *row = q >> 5; *byte = 66 + (q & 31); return 0; }
+            q -= 512;
             *row = q >> 1; *byte = q & 1; return 0;
     }
     return -1;

@@ -21,7 +21,7 @@
 #pragma once
 #include "gq_decode.cuh"
 
-// (included after the two __constant__ format tables c_iq3s_grid / c_iq4_kvalues are declared)
+// (included after the two __constant__ format tables c_iq3s_grid / c_iq3xxs_grid / c_iq4_kvalues are declared)
 namespace gq {
 
 #define GQ_PF_STAGES 4
@@ -150,7 +150,7 @@ __device__ __forceinline__ bool pf_idle(int nb, uint64_t *a_full, uint64_t *free
 template <int NB, bool SPLITK>
 __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_kernel(const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // layout: [stages x (A 16 KB | B NB*128)] [barriers] [tmem slot] [IQ3_S grid 4 KB]
+    // layout: [stages x (A 16 KB | B NB*128)] [barriers] [tmem slot] [IQ3_S and IQ3_XXS grids 6 KB]
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int B_BYTES = NB * 128;
     constexpr int STAGE = GQ_PF_A_BYTES + B_BYTES;
@@ -182,6 +182,9 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
     }
     if (d0[1] == GQ_IQ3_S || d1[1] == GQ_IQ3_S) {
         for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]);
+    }
+    if (d0[1] == GQ_IQ3_XXS || d1[1] == GQ_IQ3_XXS) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_s[GQ_IQ3XXS_GRID_OFFSET + i] = iq3s_grid_entry(c_iq3xxs_grid[i]);
     }
     if (!has1) {
         // rows 64..127 of every A stage are never written: clear them once
@@ -231,7 +234,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
         const int slab = warp - 2;                 // 0..7: rows 16*slab .. 16*slab+15 of the 128
         const int32_t *dd = (slab < 4) ? d0 : d1;
         DecAux aux;
-        aux.iq3s_grid = grid_s;
+        aux.grid = grid_s;
         {
             uint32_t tb[4];
 #pragma unroll
@@ -250,7 +253,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
 #define GQ_PF(T) case T: ok = pf_dequant<T>(tile_base, sl, row0, nkb, smem, STAGE, a_full, freeb, aux, lane); break;
             switch (dd[1]) {
                 GQ_PF(GQ_Q4_0) GQ_PF(GQ_Q5_0) GQ_PF(GQ_Q8_0) GQ_PF(GQ_Q2_K) GQ_PF(GQ_Q3_K) GQ_PF(GQ_Q4_K)
-                GQ_PF(GQ_Q5_K) GQ_PF(GQ_Q6_K) GQ_PF(GQ_IQ4_NL) GQ_PF(GQ_IQ3_S) GQ_PF(GQ_IQ4_XS)
+                GQ_PF(GQ_Q5_K) GQ_PF(GQ_Q6_K) GQ_PF(GQ_IQ4_NL) GQ_PF(GQ_IQ3_S) GQ_PF(GQ_IQ4_XS) GQ_PF(GQ_IQ3_XXS)
             }
 #undef GQ_PF
         }

@@ -250,8 +250,17 @@ class GGUFLinearMethod:
 
     # ---- a6 ----
     def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+        return self.apply_with_pre(layer, x, None, bias)
+
+    def apply_with_pre(self, layer: torch.nn.Module, x: torch.Tensor, pre, bias: torch.Tensor | None = None) -> torch.Tensor:
+        """apply of pre(x), pre being ops.PreSiluMul / ops.PreAddRMSNorm (or None): the op in front of the layer is folded
+        into the launch for up to 16 rows.  An addition to the reference's method, whose apply takes the finished
+        activation (gguf-tiles-all-types.patch:203-262)."""
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
+        if pre is not None and getattr(pre, "residual", None) is not None:
+            pre.residual = pre.residual.reshape(-1, pre.residual.shape[-1])
+            pre.residual_out = pre.residual_out.reshape(-1, pre.residual_out.shape[-1])
         tiles = getattr(layer, "gguf_tiles", None)
         groups = getattr(layer, "gguf_groups", None)
         if not tiles or not groups:
@@ -264,9 +273,9 @@ class GGUFLinearMethod:
             if idx not in groups:
                 raise RuntimeError(f"shard {idx!r} of a GGUF layer is not tiled")
             packed, descs, splits, run, nb, block_bytes = groups[idx]
-            result.append(ops.fused_mul_mat_gguf_tiles_grouped(
-                x2, packed, descs, splits, [tiles[i] for i in run], [layer.gguf_tiles_rows[i] for i in run],
-                [layer.gguf_tiles_types[i] for i in run], nb, block_bytes))
+            args = (packed, descs, splits, [tiles[i] for i in run], [layer.gguf_tiles_rows[i] for i in run],
+                    [layer.gguf_tiles_types[i] for i in run], nb, block_bytes)
+            result.append(ops.fused_mul_mat_gguf_tiles_grouped(x2, *args) if pre is None else ops.mul_mat_tiles_grouped_pre(x2, pre, *args))
             grouped.update(run)
         out = result[0] if len(result) == 1 else torch.cat(result, dim=1)
         if bias is not None:
@@ -295,5 +304,5 @@ class GGUFLinear(torch.nn.Module):
         self.quant_method.process_weights_after_loading(self)
         return self
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.quant_method.apply(self, x, self.bias)
+    def forward(self, x: torch.Tensor, pre=None) -> torch.Tensor:
+        return self.quant_method.apply_with_pre(self, x, pre, self.bias)

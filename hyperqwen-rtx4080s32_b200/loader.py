@@ -111,7 +111,7 @@ class LoadedModel:
 def load_gguf(path: str, device="cuda", strict: bool = True) -> LoadedModel:
     """Read a GGUF file and build the path's layers: one GGUFLinear per linear module of the text model, with q / k / v
     and gate / up fused as vLLM fuses them; every weight goes through GGUFLinearMethod's weight loaders and is repacked
-    tile-major on `device`.  With strict, a linear weight in a type outside the eleven raises; otherwise it is listed
+    tile-major on `device`.  With strict, a linear weight in a type the kernels do not decode raises; otherwise it is listed
     in `unsupported` and its module is left out."""
     out = LoadedModel()
     pending: dict[str, list[tuple[object, GGUFTensor]]] = {}
@@ -130,7 +130,7 @@ def load_gguf(path: str, device="cuda", strict: bool = True) -> LoadedModel:
             continue
         if t.ggml_type not in F.SUPPORTED_TYPES:
             if strict:
-                raise ValueError(f"{t.name}: GGML type {t.type_name} is not one of the eleven types of the path")
+                raise ValueError(f"{t.name}: GGML type {t.type_name} is not a type the kernels decode")
             out.unsupported[t.name] = t.type_name
             continue
         key = "lm_head" if mapped.layer is None else f"layers.{mapped.layer}.{mapped.merged or mapped.module}"
@@ -143,7 +143,7 @@ def load_gguf(path: str, device="cuda", strict: bool = True) -> LoadedModel:
         lin = GGUFLinear(k, [t.shape[0] for _, t in shards])
         for sid, t in shards:
             want = F.raw_row_bytes(t.ggml_type, k)
-            raw = torch.from_numpy(np.ascontiguousarray(t.data)).reshape(t.shape[0], -1)
+            raw = torch.from_numpy(np.array(t.data, copy=True)).reshape(t.shape[0], -1)
             if raw.shape[1] != want:
                 raise ValueError(f"{t.name}: {raw.shape[1]} bytes per row, {want} expected for {t.type_name} at K={k}")
             lin.load_shard(raw.to(device), t.ggml_type, sid)
@@ -158,7 +158,7 @@ def embedding_lookup(raw: torch.Tensor, wtype: int, ids: torch.Tensor, dtype=tor
     from . import ops
 
     if int(wtype) not in F.SUPPORTED_TYPES:
-        raise ValueError(f"GGML type {wtype} is not one of the eleven types of the path")
+        raise ValueError(f"GGML type {wtype} is not a type the kernels decode")
     k = raw.shape[1] // F.BYTES_PER_256[int(wtype)] * F.QK
     flat = ids.reshape(-1).to(raw.device)
     rows = raw.index_select(0, flat)

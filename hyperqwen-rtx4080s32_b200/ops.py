@@ -209,16 +209,56 @@ def fused_allreduce(ctx):
         _FUSED_AR = prev
 
 
+class PreSiluMul:
+    """The layer's input is silu(t[:, :K]) * t[:, K:] of the [M, 2K] tensor handed in (vLLM's silu_and_mul in front of
+    down_proj), computed inside the activation preparation."""
+    kind = 1
+
+    def unfused(self, t: torch.Tensor) -> torch.Tensor:
+        k = t.shape[-1] // 2
+        return torch.nn.functional.silu(t[..., :k]) * t[..., k:]
+
+
+class PreAddRMSNorm:
+    """The layer's input is RMSNorm(t + residual) * weight (vLLM's fused_add_rms_norm in front of qkv_proj and
+    gate_up_proj), computed inside the activation preparation; `residual_out` receives t + residual.  Without a residual,
+    plain RMSNorm."""
+    kind = 2
+
+    def __init__(self, weight: torch.Tensor, eps: float = 1e-6, residual: torch.Tensor | None = None):
+        self.weight, self.eps, self.residual = weight, float(eps), residual
+        self.residual_out = torch.empty_like(residual) if residual is not None else None
+
+    def unfused(self, t: torch.Tensor) -> torch.Tensor:
+        if self.residual is not None:
+            t = t + self.residual
+            self.residual_out.copy_(t)
+        v = t.float()
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
+        return v.to(t.dtype) * self.weight
+
+
+PRE_MAX_ROWS = 16     # the folded ops live in the integer form's preparation
+
+
 def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, split: int, wtypes: Sequence[int], n_total: int,
-                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, phases: int = 7, allreduce=None) -> torch.Tensor:
+                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, phases: int = 7, allreduce=None, pre=None) -> torch.Tensor:
     """One grouped launch for 1..64 rows: x bf16 [M, K] -> out bf16 [M, n_total] (out may be a column view).
     `workspace` (uint8, 256-byte aligned, at least gq_workspace_bytes) is allocated per call unless given;
     `phases` selects the launches (1 prepare activations, 2 grouped kernel, 4 partial sum); `allreduce` (a
-    tp.FusedAllReduce) makes the output the sum over the tensor-parallel ranks."""
+    tp.FusedAllReduce) makes the output the sum over the tensor-parallel ranks; `pre` (PreSiluMul / PreAddRMSNorm,
+    up to 16 rows) folds the op in front of the layer into the activation preparation — x is then that op's input."""
     _need_cuda(x, "x")
     if x.dtype != torch.bfloat16 or x.dim() != 2:
         raise GqError(f"x must be bf16 [M, K], got {x.dtype} {tuple(x.shape)}")
     m, k = int(x.shape[0]), int(x.shape[1])
+    if pre is not None:
+        if allreduce is not None or phases != 7 or m > PRE_MAX_ROWS:
+            raise GqError(f"a folded op needs the plain whole call and at most {PRE_MAX_ROWS} rows")
+        if pre.kind == 1:
+            if k % 2:
+                raise GqError("silu_and_mul needs an even input width")
+            k //= 2
     if m > GEMV_MAX_ROWS:
         raise GqError(f"grouped_gemm takes at most {GEMV_MAX_ROWS} rows, got {m}")
     if x.stride(1) != 1:
@@ -232,6 +272,21 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
     L = lib()
     ws_bytes = check(L.gq_workspace_bytes(m, k, n_total, int(split)), "gq_workspace_bytes")
     ws = workspace if workspace is not None else torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    if pre is not None:
+        w = res = res_out = None
+        if pre.kind == 2:
+            w, res, res_out = pre.weight, pre.residual, pre.residual_out
+            if w.dtype != torch.bfloat16 or w.numel() != k or not w.is_contiguous() or w.device != x.device:
+                raise GqError("the norm weight must be contiguous bf16 [K] on x's device")
+            if res is not None and (res.dtype != torch.bfloat16 or res.shape != x.shape or res.stride(1) != 1 or res_out.stride() != res.stride()):
+                raise GqError("the residual must be bf16 [M, K] with unit column stride")
+        with torch.cuda.device(x.device):
+            check(L.gq_gemv_grouped_pre(x.data_ptr(), m, k, x.stride(0), pre.kind, w.data_ptr() if w is not None else None,
+                                        res.data_ptr() if res is not None else None, res_out.data_ptr() if res_out is not None else None,
+                                        res.stride(0) if res is not None else 0, getattr(pre, "eps", 0.0), packed.data_ptr(), desc.data_ptr(),
+                                        int(desc.shape[0]), int(split), run_info(wtypes), out.data_ptr(), out.stride(0), n_total, ws.data_ptr(),
+                                        ws.numel(), _stream_ptr(x)), "gq_gemv_grouped_pre")
+        return out
     if allreduce is not None:
         with torch.cuda.device(x.device):
             check(L.gq_gemv_grouped_allreduce(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc.data_ptr(), int(desc.shape[0]), int(split),
@@ -280,6 +335,21 @@ def prefill_gemm(x: torch.Tensor, packed: torch.Tensor, desc1: torch.Tensor, n_t
         check(L.gq_gemm_prefill(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc1.data_ptr(), int(desc1.shape[0]), info, out.data_ptr(),
                                 out.stride(0), n_total, base, ws_bytes, _stream_ptr(x)), "gq_gemm_prefill")
     return out
+
+
+def mul_mat_tiles_grouped_pre(x: torch.Tensor, pre, packed: torch.Tensor, descs: list[torch.Tensor], desc_splits: list[int],
+                              tiles: list[torch.Tensor], n_outs: list[int], weight_types: list[int], nb: int, block_bytes: int) -> torch.Tensor:
+    """mul_mat_tiles_grouped of pre(x): up to 16 rows the op is folded into the grouped launch's activation
+    preparation; above, it runs as torch operations on the device in front of the usual call."""
+    m = int(x.shape[0])
+    if m == 0 or m > PRE_MAX_ROWS:
+        return mul_mat_tiles_grouped(pre.unfused(x), packed, descs, desc_splits, tiles, n_outs, weight_types, nb, block_bytes)
+    n_total = sum(int(n) for n in n_outs)
+    n_tiles = sum(-(-int(n) // 64) for n in n_outs)
+    s = grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=sm_count(x.device))
+    if s not in desc_splits:
+        s = 1
+    return grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, pre=pre)
 
 
 def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[torch.Tensor], desc_splits: list[int],

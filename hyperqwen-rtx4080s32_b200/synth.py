@@ -20,7 +20,8 @@ from . import formats as F
 
 # byte offsets of the fp16 d (and dmin) fields inside one GGML block
 _D_OFF = {F.Q4_0: (0,), F.Q5_0: (0,), F.Q8_0: (0,), F.IQ4_NL: (0,), F.Q2_K: (80, 82), F.Q3_K: (108,),
-          F.Q4_K: (0, 2), F.Q5_K: (0, 2), F.Q6_K: (208,), F.IQ3_S: (0,), F.IQ4_XS: (0,)}
+          F.Q4_K: (0, 2), F.Q5_K: (0, 2), F.Q6_K: (208,), F.IQ3_S: (0,), F.IQ4_XS: (0,),
+          F.IQ3_XXS: (0,), F.IQ2_XXS: (0,), F.IQ2_XS: (0,), F.IQ2_S: (0,)}
 
 
 def random_blocks(n_out: int, k: int, wtype: int, seed: int, device="cpu", d_exp: int = -6) -> torch.Tensor:
@@ -231,6 +232,49 @@ def _enc_iq3_s(w):
     return np.concatenate([dbytes.reshape(n, 2), qs, qh, signs.reshape(n, 32), scales], axis=1)
 
 
+def _nearest_grid(mag: np.ndarray, grid: np.ndarray) -> np.ndarray:
+    """Index of the nearest grid row for every row of mag [n, e]."""
+    idx = np.empty(mag.shape[0], np.int32)
+    g2 = (grid ** 2).sum(-1)
+    for i in range(0, mag.shape[0], 8192):
+        c = mag[i:i + 8192]
+        idx[i:i + 8192] = (g2[None] - 2.0 * c @ grid.T).argmin(-1)
+    return idx
+
+
+def _even_signs(wg: np.ndarray) -> np.ndarray:
+    """Sign masks (bit j set: weight j negative) of groups of eight with an even number of set bits, as the 7-bit sign index
+    plus parity can express: a group with an odd number of negatives has its smallest magnitude's sign flipped."""
+    neg = wg < 0
+    odd = neg.sum(-1) % 2 == 1
+    flip = np.abs(wg).argmin(-1)
+    rows = np.nonzero(odd)[0]
+    neg[rows, flip[rows]] ^= True
+    mask = np.zeros(wg.shape[0], np.uint8)
+    for j in range(8):
+        mask |= neg[:, j].astype(np.uint8) << j
+    return mask
+
+
+def _enc_iq3_xxs(w):
+    """d | qs[64] | u32[8]: weight = d (2 s + 1) / 4 x magnitude x sign, four magnitudes per grid index, the sign mask of a
+    group of eight stored as its low seven bits (gguf-plugin/gluon/iq3xxs.py:5-12)."""
+    from gguf.quants import IQ3_XXS
+
+    IQ3_XXS.init_grid()
+    grid = IQ3_XXS.grid.reshape(256, 4).astype(np.float32)
+    n = w.shape[0]
+    wb = w.reshape(n, 8, 32)
+    step_t = np.abs(wb).max(-1) / 48.0
+    d, dbytes = _f16(step_t.max(-1, keepdims=True) * 4.0 / 31.0)
+    s = np.clip(np.rint((_safe_div(step_t * 4.0, d) - 1.0) / 2.0), 0, 15).astype(np.uint32)
+    step = np.broadcast_to((d * (2 * s.astype(np.float32) + 1) / 4.0)[..., None], wb.shape)
+    idx = _nearest_grid(_safe_div(np.abs(wb), step).reshape(n * 64, 4), grid).reshape(n, 64)
+    signs = (_even_signs(wb.reshape(n * 32, 8)) & 0x7F).astype(np.uint32).reshape(n, 8, 4)
+    word = signs[..., 0] | (signs[..., 1] << 7) | (signs[..., 2] << 14) | (signs[..., 3] << 21) | (s << 28)
+    return np.concatenate([dbytes.reshape(n, 2), idx.astype(np.uint8), word.astype("<u4").view(np.uint8).reshape(n, 32)], axis=1)
+
+
 def _enc_gguf(wtype):
     def enc(w):
         from gguf.constants import GGMLQuantizationType
@@ -241,7 +285,7 @@ def _enc_gguf(wtype):
 
 
 _ENCODERS = {F.Q4_K: _enc_q4_k, F.Q5_K: _enc_q5_k, F.Q2_K: _enc_q2_k, F.Q3_K: _enc_q3_k, F.Q6_K: _enc_q6_k,
-             F.IQ4_NL: _enc_iq4_nl, F.IQ4_XS: _enc_iq4_xs, F.IQ3_S: _enc_iq3_s,
+             F.IQ4_NL: _enc_iq4_nl, F.IQ4_XS: _enc_iq4_xs, F.IQ3_S: _enc_iq3_s, F.IQ3_XXS: _enc_iq3_xxs,
              F.Q8_0: _enc_gguf(F.Q8_0), F.Q4_0: _enc_gguf(F.Q4_0), F.Q5_0: _enc_gguf(F.Q5_0)}
 
 

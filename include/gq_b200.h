@@ -129,6 +129,27 @@ int gq_gemv_grouped_prefetch(const void *x_dev, int64_t M, int64_t K, int64_t ld
                              void *workspace_dev, int64_t workspace_bytes, void *stream, const void *next_packed_dev,
                              int64_t next_bytes);
 
+/* gq_gemv_grouped of pre(x), the op in front of the layer folded into the activation preparation (1..16 rows):
+ *   GQ_PRE_SILU_MUL     x_dev is the [M, 2K] output of gate_up_proj (ldx >= 2K); the layer multiplies
+ *                       silu(x[:, :K]) * x[:, K:2K] — vLLM's silu_and_mul in front of down_proj;
+ *   GQ_PRE_ADD_RMSNORM  x_dev is [M, K]; the layer multiplies RMSNorm(x + residual_in) * norm_weight and
+ *                       residual_out receives x + residual_in — vLLM's fused_add_rms_norm in front of qkv_proj and
+ *                       gate_up_proj.  residual_in and residual_out (bf16 [M, ld_res]) are both given or both null
+ *                       (plain RMSNorm) and never the same memory; norm_weight_dev is bf16 [K];
+ *   GQ_PRE_NONE         gq_gemv_grouped.
+ * Intermediate values are rounded to bf16 where the unfused kernels round, so the result is that of the unfused
+ * sequence (the row's mean square is summed in another order: a last-bit difference of the normalised value can
+ * appear).  More than 16 rows: GQ_ERR_SHAPE.
+ * Reference: none — the reference serves the model with stock vLLM's separate kernels around its linear method
+ * (gguf-tiles-all-types.patch:203-262 takes the finished activation). */
+#define GQ_PRE_NONE 0
+#define GQ_PRE_SILU_MUL 1
+#define GQ_PRE_ADD_RMSNORM 2
+int gq_gemv_grouped_pre(const void *x_dev, int64_t M, int64_t K, int64_t ldx, int pre_op, const void *norm_weight_dev,
+                        const void *residual_in_dev, void *residual_out_dev, int64_t ld_res, float eps, const void *packed_dev,
+                        const int32_t *desc_dev, int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                        void *workspace_dev, int64_t workspace_bytes, void *stream);
+
 /* gq_gemv_grouped without a workspace argument, for callers that cannot allocate device memory at the
  * point of the call — a plugin op running where the framework's allocator is off limits (inside another
  * library's callback, under a fixed memory plan, or in a process that handed all of its device memory to a

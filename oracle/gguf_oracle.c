@@ -1,9 +1,10 @@
 /*
  * TEST INFRASTRUCTURE — CPU oracle for the GGUF quantized-linear path.
  *
- * A plain-C restatement of the dequantisation arithmetic of the eleven GGML block types the
+ * A plain-C restatement of the dequantisation arithmetic of the GGML block types the
  * quantized-linear method handles (Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ3_S,
- * IQ4_XS) and of the fp32 "dequantise, then multiply" result they are checked against.  Nothing in
+ * IQ4_XS, and the codebook types IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S) and of the fp32 "dequantise, then
+ * multiply" result they are checked against.  Nothing in
  * the shipped library links, loads or calls this file: only the tests, the smoke check and the
  * CPU-baseline leg of the benchmark use it, and only as the checker / the timed CPU figure.
  *
@@ -20,9 +21,10 @@
  * gguf.quants.dequantize and by the reference's own CPU model (gguf-plugin/gluon/kq_ref.py) — the
  * generating script is tests/golden/make_golden.py.
  *
- * Tables (the IQ3_S 512-entry grid and the IQ4 16-entry codebook) are not typed in here: the
- * caller loads them from the gguf package at run time (oracle_set_tables), as the reference does
- * (gguf-plugin/gluon/iq3s.py:41-52, gguf-plugin/gluon/iq4xs.py:190-206).
+ * Tables (the IQ3_S, IQ3_XXS and IQ2 grids and the IQ4 16-entry codebook) are not typed in here: the
+ * caller loads them from the gguf package at run time (oracle_set_tables, oracle_set_iq_grids), as the
+ * reference does (gguf-plugin/gluon/iq3s.py:41-52, gguf-plugin/gluon/iq4xs.py:190-206,
+ * gguf-plugin/gluon/iq2.py:8-11, gguf-plugin/gluon/iq3xxs.py:7-8).
  */
 #include <stdint.h>
 #include <string.h>
@@ -35,12 +37,22 @@
 
 enum {
     T_Q4_0 = 2, T_Q5_0 = 6, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13,
-    T_Q6_K = 14, T_IQ4_NL = 20, T_IQ3_S = 21, T_IQ4_XS = 23
+    T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ2_XS = 17, T_IQ3_XXS = 18, T_IQ4_NL = 20, T_IQ3_S = 21, T_IQ2_S = 22, T_IQ4_XS = 23
 };
 
 static uint8_t g_iq3s_grid[512][4];   /* magnitudes, odd 1..15 */
 static int8_t g_iq4_kvalues[16];
 static int g_tables_set = 0;
+static uint8_t g_iq3xxs_grid[256][4], g_iq2xxs_grid[256][8], g_iq2xs_grid[512][8], g_iq2s_grid[1024][8];
+static int g_iq_grids_set = 0;
+
+void oracle_set_iq_grids(const uint8_t *iq3xxs_256x4, const uint8_t *iq2xxs_256x8, const uint8_t *iq2xs_512x8, const uint8_t *iq2s_1024x8) {
+    memcpy(g_iq3xxs_grid, iq3xxs_256x4, sizeof g_iq3xxs_grid);
+    memcpy(g_iq2xxs_grid, iq2xxs_256x8, sizeof g_iq2xxs_grid);
+    memcpy(g_iq2xs_grid, iq2xs_512x8, sizeof g_iq2xs_grid);
+    memcpy(g_iq2s_grid, iq2s_1024x8, sizeof g_iq2s_grid);
+    g_iq_grids_set = 1;
+}
 
 void oracle_set_tables(const uint8_t *iq3s_grid_512x4, const int8_t *iq4_kvalues_16) {
     memcpy(g_iq3s_grid, iq3s_grid_512x4, sizeof g_iq3s_grid);
@@ -62,6 +74,10 @@ int oracle_bytes_per_256(int type) {
         case T_IQ4_NL: return 8 * 18;
         case T_IQ3_S: return 110;
         case T_IQ4_XS: return 136;
+        case T_IQ3_XXS: return 98;
+        case T_IQ2_XXS: return 66;
+        case T_IQ2_XS: return 74;
+        case T_IQ2_S: return 82;
         default: return 0;
     }
 }
@@ -262,6 +278,78 @@ static void deq_iq4_xs(const uint8_t *b, float *y) {
     }
 }
 
+/* The 8-bit sign mask of a group of 8 weights from its stored 7-bit index: bit 7 is the parity of the seven
+ * (llama.cpp's ksigns_iq2xs table, stated as arithmetic: gguf-plugin/gluon/iq2.py:27-28). */
+static int sign_mask8(int idx7) {
+    int p = idx7 ^ (idx7 >> 4);
+    p ^= p >> 2;
+    p ^= p >> 1;
+    return idx7 | ((p & 1) << 7);
+}
+
+/* IQ3_XXS: d | qs[64] | u32[8] (four 7-bit sign indices, scale in bits 28..31); weight = d (2 s + 1) / 4 x
+ * magnitude x sign (gguf-plugin/gluon/iq3xxs.py:5-12). */
+static void deq_iq3_xxs(const uint8_t *b, float *y) {
+    float d = f16_to_f32(b);
+    const uint8_t *qs = b + 2, *sas = b + 66;
+    for (int ib = 0; ib < 8; ib++) {
+        uint32_t w = (uint32_t)sas[4 * ib] | ((uint32_t)sas[4 * ib + 1] << 8) | ((uint32_t)sas[4 * ib + 2] << 16) | ((uint32_t)sas[4 * ib + 3] << 24);
+        float db = d * (0.5f + (float)(w >> 28)) * 0.5f;
+        for (int l = 0; l < 4; l++) {
+            int sg = sign_mask8((int)((w >> (7 * l)) & 0x7F));
+            for (int j = 0; j < 8; j++) {
+                int mag = g_iq3xxs_grid[qs[8 * ib + 2 * l + (j >> 2)]][j & 3];
+                y[32 * ib + 8 * l + j] = (db * (float)mag) * (((sg >> j) & 1) ? -1.0f : 1.0f);
+            }
+        }
+    }
+}
+
+/* IQ2_XXS: d | per sub-block two u32: four 8-bit grid indices, then four 7-bit sign indices and the scale in bits
+ * 28..31; weight = d (2 s + 1) / 8 x magnitude x sign (gguf-plugin/gluon/iq2.py:12-17). */
+static void deq_iq2_xxs(const uint8_t *b, float *y) {
+    float d = f16_to_f32(b);
+    for (int ib = 0; ib < 8; ib++) {
+        const uint8_t *q = b + 2 + 8 * ib;
+        uint32_t w = (uint32_t)q[4] | ((uint32_t)q[5] << 8) | ((uint32_t)q[6] << 16) | ((uint32_t)q[7] << 24);
+        float db = d * (0.5f + (float)(w >> 28)) * 0.25f;
+        for (int l = 0; l < 4; l++) {
+            int sg = sign_mask8((int)((w >> (7 * l)) & 0x7F));
+            for (int j = 0; j < 8; j++)
+                y[32 * ib + 8 * l + j] = (db * (float)g_iq2xxs_grid[q[l]][j]) * (((sg >> j) & 1) ? -1.0f : 1.0f);
+        }
+    }
+}
+
+/* IQ2_XS: d | u16[32]: 9-bit grid index and 7-bit sign index per group of 8 | scales[8]: a nibble per 16 weights
+ * (gguf-plugin/gluon/iq2.py:18-20). */
+static void deq_iq2_xs(const uint8_t *b, float *y) {
+    float d = f16_to_f32(b);
+    const uint8_t *qs = b + 2, *sc = b + 66;
+    for (int g = 0; g < 32; g++) {
+        int v = qs[2 * g] | (qs[2 * g + 1] << 8);
+        int s = (sc[g >> 2] >> (4 * ((g >> 1) & 1))) & 0xF;
+        float db = d * (0.5f + (float)s) * 0.25f;
+        int sg = sign_mask8(v >> 9);
+        for (int j = 0; j < 8; j++)
+            y[8 * g + j] = (db * (float)g_iq2xs_grid[v & 511][j]) * (((sg >> j) & 1) ? -1.0f : 1.0f);
+    }
+}
+
+/* IQ2_S: d | qs[32] low index bytes | signs[32] | qh[8]: two high index bits per group | scales[8] as IQ2_XS
+ * (gguf-plugin/gluon/iq2.py:21-23). */
+static void deq_iq2_s(const uint8_t *b, float *y) {
+    float d = f16_to_f32(b);
+    const uint8_t *qs = b + 2, *signs = b + 34, *qh = b + 66, *sc = b + 74;
+    for (int g = 0; g < 32; g++) {
+        int idx = qs[g] | (((qh[g >> 2] >> (2 * (g & 3))) & 3) << 8);
+        int s = (sc[g >> 2] >> (4 * ((g >> 1) & 1))) & 0xF;
+        float db = d * (0.5f + (float)s) * 0.25f;
+        for (int j = 0; j < 8; j++)
+            y[8 * g + j] = (db * (float)g_iq2s_grid[idx][j]) * (((signs[g] >> j) & 1) ? -1.0f : 1.0f);
+    }
+}
+
 /* one row segment of 256 weights -> 256 floats */
 static int deq_256(int type, const uint8_t *b, float *y) {
     switch (type) {
@@ -276,6 +364,10 @@ static int deq_256(int type, const uint8_t *b, float *y) {
         case T_Q6_K: deq_q6_k(b, y); return 0;
         case T_IQ3_S: deq_iq3_s(b, y); return 0;
         case T_IQ4_XS: deq_iq4_xs(b, y); return 0;
+        case T_IQ3_XXS: deq_iq3_xxs(b, y); return 0;
+        case T_IQ2_XXS: deq_iq2_xxs(b, y); return 0;
+        case T_IQ2_XS: deq_iq2_xs(b, y); return 0;
+        case T_IQ2_S: deq_iq2_s(b, y); return 0;
         default: return -1;
     }
 }
@@ -286,6 +378,7 @@ int oracle_dequantize(int type, const uint8_t *raw, int64_t n_rows, int64_t K, f
     if (bb == 0) return -1;
     if (K <= 0 || K % QK_K) return -2;
     if ((type == T_IQ3_S || type == T_IQ4_NL || type == T_IQ4_XS) && !g_tables_set) return -3;
+    if ((type == T_IQ3_XXS || type == T_IQ2_XXS || type == T_IQ2_XS || type == T_IQ2_S) && !g_iq_grids_set) return -3;
     int64_t nb = K / QK_K;
 #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < n_rows; r++)
@@ -304,6 +397,7 @@ int oracle_matmul(int type, const uint8_t *raw, int64_t n_rows, int64_t K, const
     if (bb == 0) return -1;
     if (K <= 0 || K % QK_K) return -2;
     if ((type == T_IQ3_S || type == T_IQ4_NL || type == T_IQ4_XS) && !g_tables_set) return -3;
+    if ((type == T_IQ3_XXS || type == T_IQ2_XXS || type == T_IQ2_XS || type == T_IQ2_S) && !g_iq_grids_set) return -3;
     int64_t nb = K / QK_K;
 #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < n_rows; r++) {

@@ -25,7 +25,7 @@ _SO = os.path.join(_HERE, "libgguf_oracle.so")
 
 TYPES = {"Q4_0": 2, "Q5_0": 6, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14,
          "IQ4_NL": 20, "IQ3_S": 21, "IQ4_XS": 23}
-BYTES_PER_256 = {2: 144, 6: 176, 8: 272, 10: 84, 11: 110, 12: 144, 13: 176, 14: 210, 20: 144, 21: 110, 23: 136}
+BYTES_PER_256 = {2: 144, 6: 176, 8: 272, 10: 84, 11: 110, 12: 144, 13: 176, 14: 210, 20: 144, 21: 110, 23: 136, 18: 98, 16: 66, 17: 74, 22: 82}
 
 _lib = None
 
@@ -43,6 +43,18 @@ def iq3s_grid_bytes() -> np.ndarray:
 
     IQ3_S.init_grid()
     return np.ascontiguousarray(IQ3_S.grid.reshape(512, 4).astype(np.uint8))
+
+
+def iq_grids() -> list[np.ndarray]:
+    """The magnitude bytes of the IQ3_XXS (256 x 4), IQ2_XXS (256 x 8), IQ2_XS (512 x 8) and IQ2_S (1024 x 8) grids, from
+    the gguf package."""
+    import gguf.quants as q
+
+    out = []
+    for cls, shape in ((q.IQ3_XXS, (256, 4)), (q.IQ2_XXS, (256, 8)), (q.IQ2_XS, (512, 8)), (q.IQ2_S, (1024, 8))):
+        cls.init_grid()
+        out.append(np.ascontiguousarray(cls.grid.reshape(shape).astype(np.uint8)))
+    return out
 
 
 def iq4_kvalues() -> np.ndarray:
@@ -65,6 +77,7 @@ def lib() -> ctypes.CDLL:
         L.oracle_num_threads.restype = ctypes.c_int
         g, kv = iq3s_grid_bytes(), iq4_kvalues()
         L.oracle_set_tables(g.ctypes.data_as(ctypes.c_void_p), kv.ctypes.data_as(ctypes.c_void_p))
+        L.oracle_set_iq_grids(*[a.ctypes.data_as(ctypes.c_void_p) for a in iq_grids()])
         _lib = L
     return _lib
 

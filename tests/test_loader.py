@@ -88,7 +88,7 @@ def test_reader_returns_the_bytes_that_were_written(tmp_path):
             assert g.ggml_type == t and g.shape == (no, kk) and np.array_equal(np.asarray(g.data).reshape(no, -1), arr)
     with pytest.raises(ValueError):
         bad = str(tmp_path / "bad.gguf")
-        _write_gguf(bad, [("blk.0.ffn_down.weight", np.zeros((64, 2 * 98), dtype=np.uint8), 18)])      # IQ3_XXS: not one of the eleven
+        _write_gguf(bad, [("blk.0.ffn_down.weight", np.zeros((64, 2 * 50), dtype=np.uint8), 19)])      # IQ1_S: a type the kernels do not decode
         loader.load_gguf(bad, device="cpu")
 
 
@@ -115,7 +115,7 @@ def test_layers_loaded_from_a_gguf_file_match_the_oracle(tmp_path):
             assert oracle.rel_err(y, ref) < 6e-3, (key, m)
     # the embedding stays raw; looking rows up is a gather + the bit-exact dequantiser
     emb = model.embedding
-    table = torch.from_numpy(np.ascontiguousarray(emb.data)).reshape(emb.shape[0], -1).to(dev)
+    table = torch.from_numpy(np.array(emb.data, copy=True)).reshape(emb.shape[0], -1).to(dev)
     ids = torch.tensor([[0, 999, 17], [17, 5, 640]], device=dev)
     got = loader.embedding_lookup(table, emb.ggml_type, ids, dtype=torch.float32).cpu().numpy()
     want = oracle.dequantize(raw["token_embd.weight"], F.Q8_0)[ids.cpu().numpy().reshape(-1)].reshape(2, 3, -1)
