@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(256) unrepack_kernel(int type, int B, const ui
 // ---------------------------------------------------------------------------------------------------
 __constant__ uint32_t c_iq3s_grid[512];
 __constant__ uint32_t c_iq3xxs_grid[256];
+__constant__ uint32_t c_iq2xxs_grid[512], c_iq2xs_grid[1024], c_iq2s_grid[2048];    // two words per entry
 __constant__ int8_t c_iq4_kvalues[16];
 
 // A bounded wait that runs out is reported twice: in the status word of the launch's workspace (gq_read_status) and in
@@ -185,6 +186,24 @@ __device__ float deq_one(int type, const uint8_t *b, int w) {
             const uint32_t f = (sw >> (7 * (j >> 3))) & 0x7Fu, mask = f | (((uint32_t)__popc(f) & 1u) << 7);
             const float mag = (float)((c_iq3xxs_grid[b[2 + 8 * ib + (j >> 2)]] >> (8 * (j & 3))) & 0xFF);
             const float v = __fmul_rn(db, mag); return ((mask >> (j & 7)) & 1) ? -v : v; }
+        case GQ_IQ2_XXS: { const int ib = w >> 5, j = w & 31, l = j >> 3; const uint8_t *q = b + 2 + 8 * ib;
+            const uint32_t sw = q[4] | (q[5] << 8) | (q[6] << 16) | ((uint32_t)q[7] << 24);
+            const float db = __fmul_rn(__fmul_rn(h2f(b), 0.5f + (float)(sw >> 28)), 0.25f);
+            const uint32_t f = (sw >> (7 * l)) & 0x7Fu, mask = f | (((uint32_t)__popc(f) & 1u) << 7);
+            const float mag = (float)((c_iq2xxs_grid[2 * q[l] + ((j >> 2) & 1)] >> (8 * (j & 3))) & 0xFF);
+            const float v = __fmul_rn(db, mag); return ((mask >> (j & 7)) & 1) ? -v : v; }
+        case GQ_IQ2_XS: { const int g = w >> 3, j = w & 7; const uint32_t hw = b[2 + 2 * g] | (b[3 + 2 * g] << 8);
+            const int sc = (b[66 + (g >> 2)] >> (4 * ((g >> 1) & 1))) & 0xF;
+            const float db = __fmul_rn(__fmul_rn(h2f(b), 0.5f + (float)sc), 0.25f);
+            const uint32_t f = hw >> 9, mask = f | (((uint32_t)__popc(f) & 1u) << 7);
+            const float mag = (float)((c_iq2xs_grid[2 * (hw & 511u) + (j >> 2)] >> (8 * (j & 3))) & 0xFF);
+            const float v = __fmul_rn(db, mag); return ((mask >> j) & 1) ? -v : v; }
+        case GQ_IQ2_S: { const int g = w >> 3, j = w & 7;
+            const uint32_t idx = b[2 + g] | (((uint32_t)(b[66 + (g >> 2)] >> (2 * (g & 3))) & 3u) << 8);
+            const int sc = (b[74 + (g >> 2)] >> (4 * ((g >> 1) & 1))) & 0xF;
+            const float db = __fmul_rn(__fmul_rn(h2f(b), 0.5f + (float)sc), 0.25f);
+            const float mag = (float)((c_iq2s_grid[2 * idx + (j >> 2)] >> (8 * (j & 3))) & 0xFF);
+            const float v = __fmul_rn(db, mag); return ((b[34 + g] >> j) & 1) ? -v : v; }
         case GQ_IQ4_XS: { const int ib = w >> 5, j = w & 31; const uint32_t sh = b[2] | (b[3] << 8);
             const int ls = (int)(((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
             const float dl = __fmul_rn(h2f(b), (float)ls);
@@ -577,7 +596,7 @@ struct GemvParams {
     int M, K, nb, split, stages;
     int64_t ldy, n_total;
     int wbytes_max;      // largest tile bytes in the launch (stage stride of the weight buffers)
-    int has_iq3s;
+    int cb_bytes;                    // shared-memory bytes of the codebook-table region (0: the run has no codebook type)
     int cluster;         // 1: the `split` CTAs of a tile form a thread-block cluster and reduce through shared memory
     int cluster_push;    // 1: the others store their accumulators into slots of the split-0 CTA's shared memory (one cluster barrier)
     const uint8_t *pf_ptr;   // weights the caller will multiply next (or null): prefetched into L2 while this launch computes
@@ -953,8 +972,6 @@ __device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const ui
 // for launches whose shards all share it (a smaller kernel; most launches of a real model are such).
 template <int MT, int FORM>
 __host__ __device__ constexpr int gq_stage_xbytes() { return FORM ? 8 * MT * GQ_X8_ROW + 32 * MT : 8 * MT * GQ_XROW_BYTES; }
-template <int FORM>
-__host__ __device__ constexpr int gq_iq3s_smem() { return FORM ? GQ_IQ3S8_SMEM_BYTES : GQ_IQ3S_SMEM_BYTES; }
 
 template <int MT, int MINB, int FORM, int ONLY>
 __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_grouped_kernel(const __grid_constant__ GemvParams p) {
@@ -976,6 +993,13 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     const int tile_bytes = 64 * B;
     const int nk = kb1 - kb0;
 
+    // a tile whose type contradicts the call's run_info (not the single type it named, or a codebook type it did not
+    // announce, which has no table space): report and leave (every CTA of a cluster works on the same tile, so a cluster
+    // leaves as one)
+    if ((ONLY != 0 && d[1] != ONLY) || (gq_cb_kind(type) >= 0 && gq_cb_bytes(gq_cb_kind(type), FORM) > p.cb_bytes)) {
+        if (threadIdx.x == 0) { pdl_wait(); report_status(p.status, GQ_DEV_BAD_SHAPE); }      // after the preparation kernel has cleared the word
+        return;
+    }
     Ring ring;
     ring.smem = smem; ring.full = full; ring.empty = empty;
     ring.stages = stages; ring.stage_bytes = stage_bytes; ring.wmax = wmax; ring.nk = nk;
@@ -984,16 +1008,27 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, GQ_CONSUMER_WARPS); }
         fence_barrier_init();
     }
-    if ((ONLY == 0 || ONLY == GQ_IQ3_S) && p.has_iq3s && type == GQ_IQ3_S) {
-        if constexpr (FORM) { for (int i = threadIdx.x; i < 512; i += blockDim.x) reinterpret_cast<uint32_t *>(grid_s)[i] = iq3s_grid_entry8(c_iq3s_grid[i]); }
-        else { for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]); }
-    }
-    if ((ONLY == 0 || ONLY == GQ_IQ3_XXS) && p.has_iq3s && type == GQ_IQ3_XXS) {
-        if constexpr (FORM) {
-            uint32_t *g8 = reinterpret_cast<uint32_t *>(grid_s);
-            for (int i = threadIdx.x; i < 256; i += blockDim.x) { g8[i] = iq3s_grid_entry8(c_iq3xxs_grid[i]); g8[256 + i] = iq3xxs_sign_entry8((uint32_t)i); }
-        } else {
-            for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_s[GQ_IQ3XXS_GRID_OFFSET + i] = iq3s_grid_entry(c_iq3xxs_grid[i]);
+    // the codebook table of this CTA's type, at the start of the table region
+    if (p.cb_bytes) {
+        uint32_t *g32 = reinterpret_cast<uint32_t *>(grid_s);
+        if ((ONLY == 0 || ONLY == GQ_IQ3_S) && type == GQ_IQ3_S) {
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 512; i += blockDim.x) g32[i] = iq3s_grid_entry8(c_iq3s_grid[i]); }
+            else { for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]); }
+        }
+        if ((ONLY == 0 || ONLY == GQ_IQ3_XXS) && type == GQ_IQ3_XXS) {
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += blockDim.x) { g32[i] = iq3s_grid_entry8(c_iq3xxs_grid[i]); g32[256 + i] = iq3xxs_sign_entry8((uint32_t)i); } }
+            else { for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3xxs_grid[i]); }
+        }
+        if ((ONLY == 0 || ONLY == GQ_IQ2_XXS) && type == GQ_IQ2_XXS) {
+            for (int i = threadIdx.x; i < 512; i += blockDim.x) g32[i] = iq3s_grid_entry8(c_iq2xxs_grid[i]);
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += blockDim.x) g32[512 + i] = iq3xxs_sign_entry8((uint32_t)i); }
+        }
+        if ((ONLY == 0 || ONLY == GQ_IQ2_XS) && type == GQ_IQ2_XS) {
+            for (int i = threadIdx.x; i < 1024; i += blockDim.x) g32[i] = iq3s_grid_entry8(c_iq2xs_grid[i]);
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += blockDim.x) g32[1024 + i] = iq3xxs_sign_entry8((uint32_t)i); }
+        }
+        if ((ONLY == 0 || ONLY == GQ_IQ2_S) && type == GQ_IQ2_S) {
+            for (int i = threadIdx.x; i < 2048; i += blockDim.x) g32[i] = iq3s_grid_entry8(c_iq2s_grid[i]);
         }
     }
     __syncthreads();
@@ -1078,6 +1113,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             switch (type) {
                 GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
                 GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS) GQ_CONSUME(GQ_IQ3_XXS)
+                GQ_CONSUME(GQ_IQ2_XXS) GQ_CONSUME(GQ_IQ2_XS) GQ_CONSUME(GQ_IQ2_S)
             }
         }
 #undef GQ_CONSUME
@@ -1089,6 +1125,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         switch (type) {
             GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
             GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS) GQ_CONSUME(GQ_IQ3_XXS)
+                GQ_CONSUME(GQ_IQ2_XXS) GQ_CONSUME(GQ_IQ2_XS) GQ_CONSUME(GQ_IQ2_S)
         }
 #undef GQ_CONSUME
     }
@@ -1097,7 +1134,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     // ---- epilogue: rows of the MMA are output columns, columns of the MMA are batch rows ----
     const int g = lane >> 2, t = lane & 3;
     // scratch of its own behind the ring (a slower warp may still read the ring): GQ_CONSUMER_WARPS x MT x 512 bytes
-    float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + (p.has_iq3s ? gq_iq3s_smem<FORM>() : 0));
+    float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(grid_s) + p.cb_bytes);
     if (push) {
         cluster_wait();         // the rendezvous entered at the start: every CTA of the cluster is running
         // split-K inside a cluster, push form: the CTAs of splits 1.. store their accumulators into their slot of the
@@ -1199,6 +1236,9 @@ static int ensure_tables() {
     if (dev < 64 && (done_mask.load() >> dev) & 1ull) return GQ_OK;
     GQ_CUDA(cudaMemcpyToSymbol(c_iq3s_grid, GQ_IQ3S_GRID, sizeof GQ_IQ3S_GRID));
     GQ_CUDA(cudaMemcpyToSymbol(c_iq3xxs_grid, GQ_IQ3XXS_GRID, sizeof GQ_IQ3XXS_GRID));
+    GQ_CUDA(cudaMemcpyToSymbol(c_iq2xxs_grid, GQ_IQ2XXS_GRID, sizeof GQ_IQ2XXS_GRID));
+    GQ_CUDA(cudaMemcpyToSymbol(c_iq2xs_grid, GQ_IQ2XS_GRID, sizeof GQ_IQ2XS_GRID));
+    GQ_CUDA(cudaMemcpyToSymbol(c_iq2s_grid, GQ_IQ2S_GRID, sizeof GQ_IQ2S_GRID));
     GQ_CUDA(cudaMemcpyToSymbol(c_iq4_kvalues, GQ_IQ4_KVALUES, sizeof GQ_IQ4_KVALUES));
     if (dev < 64) done_mask.fetch_or(1ull << dev);
     return GQ_OK;
@@ -1319,7 +1359,7 @@ template <int MT, int MINB, int FORM, int ONLY>
 static int launch_gemv(const GemvParams &p, int64_t n_desc, cudaStream_t stream) {
     constexpr int xbytes = gq_stage_xbytes<MT, FORM>();
     const int stage_bytes = p.wbytes_max + xbytes;
-    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (p.has_iq3s ? gq_iq3s_smem<FORM>() : 0) +
+    const size_t smem = (size_t)p.stages * stage_bytes + (size_t)p.stages * 16 + (size_t)p.cb_bytes +
                         (size_t)GQ_CONSUMER_WARPS * MT * 512 * (p.cluster_push ? p.split - 1 : 1);
     if (smem > 232448) return GQ_ERR_LIMIT;
     // opt in once per device to the largest dynamic shared memory a CTA can have
@@ -1355,7 +1395,7 @@ static int launch_gemv8_m8(const GemvParams &p, int64_t n_desc, cudaStream_t st,
     switch (only) {
 #define GQ_ONE(T) case T: return launch_gemv<1, 4, 1, T>(p, n_desc, st);
         GQ_ONE(GQ_Q4_0) GQ_ONE(GQ_Q5_0) GQ_ONE(GQ_Q8_0) GQ_ONE(GQ_Q2_K) GQ_ONE(GQ_Q3_K) GQ_ONE(GQ_Q4_K)
-        GQ_ONE(GQ_Q5_K) GQ_ONE(GQ_Q6_K) GQ_ONE(GQ_IQ4_NL) GQ_ONE(GQ_IQ3_S) GQ_ONE(GQ_IQ4_XS) GQ_ONE(GQ_IQ3_XXS)
+        GQ_ONE(GQ_Q5_K) GQ_ONE(GQ_Q6_K) GQ_ONE(GQ_IQ4_NL) GQ_ONE(GQ_IQ3_S) GQ_ONE(GQ_IQ4_XS) GQ_ONE(GQ_IQ3_XXS) GQ_ONE(GQ_IQ2_XXS) GQ_ONE(GQ_IQ2_XS) GQ_ONE(GQ_IQ2_S)
 #undef GQ_ONE
         default: return launch_gemv<1, 4, 1, 0>(p, n_desc, st);
     }
@@ -1363,15 +1403,15 @@ static int launch_gemv8_m8(const GemvParams &p, int64_t n_desc, cudaStream_t st,
 
 extern "C" int gq_run_info(int n_shards, const int32_t *types) {
     if (n_shards <= 0 || !types) return GQ_ERR_ARG;
-    int maxb = 0, iq3s = 0, single = types[0];
+    int maxb = 0, cb = 0, single = types[0];
     for (int i = 0; i < n_shards; ++i) {
         const int B = gq_type_bytes(types[i]);
         if (!B) return GQ_ERR_TYPE;
         if (B > maxb) maxb = B;
-        if (types[i] == GQ_IQ3_S || types[i] == GQ_IQ3_XXS) iq3s = 1;      // a codebook type: the kernels keep its grid in shared memory
+        if (gq_cb_kind(types[i]) >= 0) cb |= 1 << gq_cb_kind(types[i]);     // a codebook type: the kernels keep its grid in shared memory
         if (types[i] != single) single = 0;
     }
-    return maxb | (iq3s << 16) | (single << 17);
+    return maxb | ((cb ? 1 : 0) << 16) | (single << 17) | (cb << 22);
 }
 
 static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
@@ -1420,9 +1460,9 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     p.y = (__nv_bfloat16 *)y_dev; p.partials = ws.partials; p.status = ws.status;
     p.M = (int)M; p.K = (int)K; p.nb = (int)(K / GQ_QK); p.split = split; p.ldy = ldy; p.n_total = n_total;
     const int maxb = run_info & 0xFFFF;
-    if (maxb < 84 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
+    if (maxb < 66 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
     p.wbytes_max = 64 * maxb;   // every stage can hold a tile of any shard of the run
-    p.has_iq3s = (run_info >> 16) & 1;
+    p.cb_bytes = gq_cb_region_max((run_info >> 22) & 31, form);
     // split-K up to 8 reduces inside a thread-block cluster (portable cluster size); larger splits keep the fp32
     // partials and the separate sum
     p.cluster = (split > 1 && split <= 8 && n_desc % split == 0) ? 1 : 0;
@@ -1443,7 +1483,7 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
         const int xb = !form ? 8 * mt * GQ_XROW_BYTES : mt == 1 ? gq_stage_xbytes<1, 1>() : mt == 2 ? gq_stage_xbytes<2, 1>() : gq_stage_xbytes<4, 1>();
         const int stage_bytes = p.wbytes_max + xb;
         // (an SM has 228 KB of shared memory and the system keeps 1 KB of it per resident CTA)
-        const int fixed = 64 + (p.has_iq3s ? (form ? GQ_IQ3S8_SMEM_BYTES : GQ_IQ3S_SMEM_BYTES) : 0) + 1024, red1 = GQ_CONSUMER_WARPS * mt * 512;
+        const int fixed = 64 + p.cb_bytes + 1024, red1 = GQ_CONSUMER_WARPS * mt * 512;
         // split-K in a cluster: the push form of the reduction needs a scratch slot per other split in every CTA; it
         // is used when that costs no resident CTA (the ring then has three stages; its depth does not matter)
         if (p.cluster) {
@@ -1757,13 +1797,14 @@ extern "C" int64_t gq_prefill_workspace_bytes(int64_t M, int64_t K, int64_t n_to
 template <int NB>
 static int launch_prefill(PrefillParams &p, const __nv_bfloat16 *x, int64_t ldx, float *ex, uint8_t *xp, cudaStream_t st) {
     const int mt = (p.M + NB - 1) / NB;
-    const size_t smem = 1024 + (size_t)GQ_PF_STAGES * (GQ_PF_A_BYTES + NB * 128) + 128 + GQ_IQ3S_SMEM_BYTES;
+    const size_t smem_base = 1024 + (size_t)GQ_PF_STAGES * (GQ_PF_A_BYTES + NB * 128) + 128;
+    const size_t smem = smem_base + (size_t)gq_cb_region_sum(p.cb_mask), smem_max = smem_base + (size_t)gq_cb_region_sum(31);
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !((done_mask.load() >> dev) & 1ull)) {
-        GQ_CUDA(cudaFuncSetAttribute(gemm_prefill_kernel<NB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        GQ_CUDA(cudaFuncSetAttribute(gemm_prefill_kernel<NB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        GQ_CUDA(cudaFuncSetAttribute(gemm_prefill_kernel<NB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+        GQ_CUDA(cudaFuncSetAttribute(gemm_prefill_kernel<NB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
         if (dev < 64) done_mask.fetch_or(1ull << dev);
     }
     prep_x_prefill_kernel<NB><<<(unsigned)(mt * NB), 256, 0, st>>>(x, ldx, p.K, p.M, ex, xp, p.status);
@@ -1789,7 +1830,7 @@ extern "C" int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t 
         return GQ_ERR_ARG;
     if (n_desc > 0x7ffffffe || M > (int64_t)65535 * 64) return GQ_ERR_LIMIT;
     const int maxb = run_info & 0xFFFF;
-    if (maxb < 84 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
+    if (maxb < 66 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
     const int nbt = prefill_nb(M);
     const int split = prefill_split(n_desc, M, K / GQ_QK, nbt, device_sms());
     int *status; float *ex; uint8_t *xp; float *partials;
@@ -1799,7 +1840,7 @@ extern "C" int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t 
     PrefillParams p;
     p.packed = (const uint8_t *)packed_dev; p.desc = desc_dev; p.n_desc = (int)n_desc; p.xp = xp; p.ex = ex;
     p.y = (__nv_bfloat16 *)y_dev; p.ldy = ldy; p.M = (int)M; p.K = (int)K; p.nb = (int)(K / GQ_QK); p.status = status;
-    p.split = split; p.partials = partials; p.n_total = n_total;
+    p.split = split; p.partials = partials; p.n_total = n_total; p.cb_mask = (run_info >> 22) & 31;
     cudaStream_t st = (cudaStream_t)stream;
     switch (nbt) {
         case 64: return launch_prefill<64>(p, (const __nv_bfloat16 *)x_dev, ldx, ex, xp, st);

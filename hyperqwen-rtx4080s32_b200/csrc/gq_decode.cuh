@@ -70,7 +70,8 @@ GQ_HD inline void iq4_word(uint32_t w, const Iq4Table &T, uint32_t (&lo)[2], uin
 GQ_HD inline uint32_t bytes_h2(uint32_t w, uint32_t sel) { return prmt(w, GQ_MAGICB, sel); }
 
 struct DecAux {
-    const uint2 *grid;        // shared memory: the codebook of the CTA's type (IQ3_S 512, IQ3_XXS 256 entries), {fp16(m0,m1), fp16(m2,m3)}
+    const uint2 *grid;        // shared memory: the codebook of the type being decoded — IQ3_S (512) / IQ3_XXS (256) entries
+                              // {fp16(m0,m1), fp16(m2,m3)}; IQ2_*: 8 magnitude bytes per entry, each word in quad byte order
     Iq4Table iq4;
 };
 
@@ -636,10 +637,7 @@ struct Dec<GQ_Q3_K> {
     template <int R> static constexpr float offs() { return float((1024 >> (2 * ((R >> 1) & 3))) + 4); }
 };
 
-// fp16 form: the IQ3_S grid (512 x 8 bytes) followed by the IQ3_XXS grid (256 x 8 bytes); a CTA fills the tables of
-// the types it decodes (the tcgen05 kernel's two tiles may differ in type)
-#define GQ_IQ3S_SMEM_BYTES 6144
-#define GQ_IQ3XXS_GRID_OFFSET 512
+
 // ---- IQ3_S ----------------------------------------------------------------------------------------
 template <>
 struct Dec<GQ_IQ3_S> {
@@ -715,7 +713,7 @@ struct Dec<GQ_IQ3_XXS> {
     int sh0, shn;        // 7 (t >> 1): the lane's sign index inside a half sub-block; 4 (t & 1): its nibble of the mask
     const uint2 *grid;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
-        grid = aux.grid + GQ_IQ3XXS_GRID_OFFSET;
+        grid = aux.grid;
         const int t = lane & 3;
         sh0 = 7 * (t >> 1);
         shn = 4 * (t & 1);
@@ -754,6 +752,175 @@ struct Dec<GQ_IQ3_XXS> {
         s1 = u32_as_f32(0x4B000001u + 2u * (sw[1][G] >> 28)) - 8388608.0f;
     }
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.25f * f16bits(dd[0]); d1 = 0.25f * f16bits(dd[1]); }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 0.0f; }
+};
+
+// ---- IQ2_XXS / IQ2_XS / IQ2_S: eight magnitudes per grid entry, shared by two lanes; weight = d (2 s + 1) / 8 x
+// magnitude x sign (gguf-plugin/gluon/iq2.py:6-23).  The shared-memory grid is the integer form's (bytes in quad order
+// (0,2,1,3) per word); the bytes become fp16 through the 1024 + byte pattern. ----
+GQ_HD inline uint32_t pick_alt_bytes16(uint32_t a, uint32_t b, int tp) { return prmt(a, b, 0x6420u + 0x1111u * (uint32_t)tp); }
+// the lane's word e of a grid entry and its four sign bits -> the fp16 pairs (w0, w1), (w2, w3)
+GQ_HD inline void iq2_pairs(uint32_t e, uint32_t nib, uint32_t &a01, uint32_t &a23) {
+    a01 = xor_and(hsub2(prmt(e, GQ_MAGICB, 0x5250u), h2k(1024)), nib * 0x40008000u, 0x80008000u);
+    a23 = xor_and(hsub2(prmt(e, GQ_MAGICB, 0x5351u), h2k(1024)), (nib >> 2) * 0x40008000u, 0x80008000u);
+}
+GQ_HD inline float odd_scale_f32(uint32_t s) { return u32_as_f32(0x4B000001u + 2u * s) - 8388608.0f; }    // 2 s + 1
+
+template <>
+struct Dec<GQ_IQ2_XXS> {
+    static constexpr int GROUP = 32;
+    static constexpr int NCORR = 0;
+    uint32_t q[2][4];    // grid-index byte of run r in byte r & 3 of word r >> 2
+    uint32_t sw[2][8];
+    uint32_t dd[2];
+    int sh0, shn;
+    const uint8_t *grid;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
+        const int t = lane & 3, tp = t >> 1;
+        grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
+        sh0 = 7 * tp;
+        shn = 4 * (t & 1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            const uint4 ia = ld16(slab + 32 * row), ib = ld16(slab + 32 * row + 16);
+            q[h][0] = pick_alt_bytes16(ia.x, ia.y, tp); q[h][1] = pick_alt_bytes16(ia.z, ia.w, tp);
+            q[h][2] = pick_alt_bytes16(ib.x, ib.y, tp); q[h][3] = pick_alt_bytes16(ib.z, ib.w, tp);
+            const uint4 a = ld16(slab + 512 + 32 * row), b = ld16(slab + 528 + 32 * row);
+            sw[h][0] = a.x; sw[h][1] = a.y; sw[h][2] = a.z; sw[h][3] = a.w;
+            sw[h][4] = b.x; sw[h][5] = b.y; sw[h][6] = b.z; sw[h][7] = b.w;
+            dd[h] = ld2(slab + 1024 + 2 * row);
+        }
+    }
+    template <int R>
+    GQ_HD void run(int h, uint32_t &a01, uint32_t &a23) const {
+        const uint32_t idx = (q[h][R >> 2] >> (8 * (R & 3))) & 0xFFu;
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + 8 * idx);
+        const uint32_t f = (sw[h][R >> 1] >> (14 * (R & 1) + sh0)) & 0x7Fu;
+        const uint32_t mask = f | (popc32(f) << 7);
+        iq2_pairs(e, (mask >> shn) & 0xFu, a01, a23);
+    }
+    template <int P>
+    GQ_HD void pair(uint32_t (&a)[2][4]) const {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            run<2 * P>(h, a[0][h], a[0][2 + h]);
+            run<2 * P + 1>(h, a[1][h], a[1][2 + h]);
+        }
+    }
+    template <int G>
+    GQ_HD void scale(float &s0, float &s1) const { s0 = odd_scale_f32(sw[0][G] >> 28); s1 = odd_scale_f32(sw[1][G] >> 28); }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 0.0f; }
+};
+
+template <>
+struct Dec<GQ_IQ2_XS> {
+    static constexpr int GROUP = 16;
+    static constexpr int NCORR = 0;
+    uint32_t v[2][8];    // the halfword (9-bit grid index, 7-bit sign index) of run r in half r & 1 of word r >> 1
+    uint2 sc[2];         // scales[8] of the row: byte ib = nibbles of runs 2 ib, 2 ib + 1
+    uint32_t dd[2];
+    int shn;
+    const uint8_t *grid;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
+        const int t = lane & 3, tp = t >> 1;
+        grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
+        shn = 4 * (t & 1);
+        const uint32_t sel = 0x5410u + 0x2222u * (uint32_t)tp;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint4 w = ld16(slab + 64 * row + 16 * c);
+                v[h][2 * c] = prmt(w.x, w.y, sel);
+                v[h][2 * c + 1] = prmt(w.z, w.w, sel);
+            }
+            sc[h] = ld8(slab + 1024 + 8 * row);
+            dd[h] = ld2(slab + 1152 + 2 * row);
+        }
+    }
+    template <int R>
+    GQ_HD void run(int h, uint32_t &a01, uint32_t &a23) const {
+        const uint32_t hw = (v[h][R >> 1] >> (16 * (R & 1))) & 0xFFFFu;
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + 8 * (hw & 511u));
+        const uint32_t f = hw >> 9;
+        const uint32_t mask = f | (popc32(f) << 7);
+        iq2_pairs(e, (mask >> shn) & 0xFu, a01, a23);
+    }
+    template <int P>
+    GQ_HD void pair(uint32_t (&a)[2][4]) const {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            run<2 * P>(h, a[0][h], a[0][2 + h]);
+            run<2 * P + 1>(h, a[1][h], a[1][2 + h]);
+        }
+    }
+    template <int G>
+    GQ_HD void scale(float &s0, float &s1) const {
+        constexpr int ib = G >> 1, sh = 8 * (ib & 3) + 4 * (G & 1);
+        s0 = odd_scale_f32((((ib < 4) ? sc[0].x : sc[0].y) >> sh) & 0xFu);
+        s1 = odd_scale_f32((((ib < 4) ? sc[1].x : sc[1].y) >> sh) & 0xFu);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 0.0f; }
+};
+
+template <>
+struct Dec<GQ_IQ2_S> {
+    static constexpr int GROUP = 16;
+    static constexpr int NCORR = 0;
+    uint32_t q[2][4], sg[2][4];   // low index byte / the lane's sign nibble of run r in byte r & 3 of word r >> 2
+    uint2 qh[2], sc[2];
+    uint32_t dd[2];
+    const uint8_t *grid;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
+        const int t = lane & 3, tp = t >> 1, sh = 4 * (t & 1);
+        grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            const uint4 ia = ld16(slab + 32 * row), ib = ld16(slab + 32 * row + 16);
+            q[h][0] = pick_alt_bytes16(ia.x, ia.y, tp); q[h][1] = pick_alt_bytes16(ia.z, ia.w, tp);
+            q[h][2] = pick_alt_bytes16(ib.x, ib.y, tp); q[h][3] = pick_alt_bytes16(ib.z, ib.w, tp);
+            const uint4 sa = ld16(slab + 512 + 32 * row), sb = ld16(slab + 512 + 32 * row + 16);
+            sg[h][0] = (pick_alt_bytes16(sa.x, sa.y, tp) >> sh) & 0x0f0f0f0fu; sg[h][1] = (pick_alt_bytes16(sa.z, sa.w, tp) >> sh) & 0x0f0f0f0fu;
+            sg[h][2] = (pick_alt_bytes16(sb.x, sb.y, tp) >> sh) & 0x0f0f0f0fu; sg[h][3] = (pick_alt_bytes16(sb.z, sb.w, tp) >> sh) & 0x0f0f0f0fu;
+            uint2 hq = ld8(slab + 1024 + 8 * row);
+            hq.x >>= 2 * tp; hq.y >>= 2 * tp;
+            qh[h] = hq;
+            sc[h] = ld8(slab + 1152 + 8 * row);
+            dd[h] = ld2(slab + 1280 + 2 * row);
+        }
+    }
+    template <int R>
+    GQ_HD void run(int h, uint32_t &a01, uint32_t &a23) const {
+        constexpr int ib = R >> 1, u = R & 1;
+        const uint32_t idxb = (q[h][R >> 2] >> (8 * (R & 3))) & 0xFFu;
+        const uint32_t hw = (ib < 4) ? qh[h].x : qh[h].y;
+        const uint32_t idx = or_and(idxb, shl_c<8 - (8 * (ib & 3) + 4 * u)>(hw), 0x300u);
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + 8 * idx);
+        iq2_pairs(e, (sg[h][R >> 2] >> (8 * (R & 3))) & 0xFu, a01, a23);
+    }
+    template <int P>
+    GQ_HD void pair(uint32_t (&a)[2][4]) const {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            run<2 * P>(h, a[0][h], a[0][2 + h]);
+            run<2 * P + 1>(h, a[1][h], a[1][2 + h]);
+        }
+    }
+    template <int G>
+    GQ_HD void scale(float &s0, float &s1) const {
+        constexpr int ib = G >> 1, sh = 8 * (ib & 3) + 4 * (G & 1);
+        s0 = odd_scale_f32((((ib < 4) ? sc[0].x : sc[0].y) >> sh) & 0xFu);
+        s1 = odd_scale_f32((((ib < 4) ? sc[1].x : sc[1].y) >> sh) & 0xFu);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
     static constexpr bool HAS_MIN = false;
     template <int R> static constexpr float offs() { return 0.0f; }
 };

@@ -578,4 +578,163 @@ struct Dec8<GQ_IQ3_XXS> {
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.25f * f16bits(dd[0]); d1 = 0.25f * f16bits(dd[1]); }
 };
 
+// ---- IQ2_XXS / IQ2_XS / IQ2_S --------------------------------------------------------------------------
+// A grid entry holds eight magnitudes; the lanes t = 0, 1 (2, 3) of a row share the entry of the first (second) eight
+// weights of a run and take its word t & 1.  Shared memory: the grid as two words per entry, each in quad byte order,
+// then (IQ2_XXS, IQ2_XS) the 128 x 2 sign words of IQ3_XXS.  weight = d (2 s + 1) / 8 x magnitude x sign
+// (gguf-plugin/gluon/iq2.py:6-23).
+
+// bytes tp, 2 + tp of two words -> one word (runtime tp): the even or the odd bytes of eight
+GQ_HD inline uint32_t pick_alt_bytes(uint32_t a, uint32_t b, int tp) { return prmt(a, b, 0x6420u + 0x1111u * (uint32_t)tp); }
+
+template <>
+struct Dec8<GQ_IQ2_XXS> {
+    static constexpr int SCHEME = GQ_S32;
+    static constexpr bool A_SIGNED = true;
+    static constexpr int NCORR = 0;
+    uint32_t q[2][4];    // grid-index byte of run r in byte r & 3 of word r >> 2
+    uint32_t sw[2][8];   // the sign-and-scale word of each sub-block
+    uint32_t dd[2];
+    int rot0, rot1;
+    const uint8_t *grid, *signs;    // both offset by the lane's half of an entry
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
+        const int t = lane & 3, tp = t >> 1;
+        grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
+        signs = reinterpret_cast<const uint8_t *>(aux.grid + 512) + 4 * (t & 1);
+        rot0 = (7 * tp - 3) & 31;
+        rot1 = 7 * (2 + tp) - 3;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            const uint4 ia = ld16(slab + 32 * row), ib = ld16(slab + 32 * row + 16);
+            // index word of sub-block ib: bytes l = 0..3; run 2 ib + u takes byte 2 u + tp
+            q[h][0] = pick_alt_bytes(ia.x, ia.y, tp); q[h][1] = pick_alt_bytes(ia.z, ia.w, tp);
+            q[h][2] = pick_alt_bytes(ib.x, ib.y, tp); q[h][3] = pick_alt_bytes(ib.z, ib.w, tp);
+            const uint4 a = ld16(slab + 512 + 32 * row), b = ld16(slab + 528 + 32 * row);
+            sw[h][0] = a.x; sw[h][1] = a.y; sw[h][2] = a.z; sw[h][3] = a.w;
+            sw[h][4] = b.x; sw[h][5] = b.y; sw[h][6] = b.z; sw[h][7] = b.w;
+            dd[h] = ld2(slab + 1024 + 2 * row);
+        }
+    }
+    template <int R, int H>
+    GQ_HD uint32_t quad() const {
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + 8 * (uint32_t)ubyte<(R & 3)>(q[H][R >> 2]));
+        const uint32_t w = sw[H][R >> 1];
+        const uint32_t one = *reinterpret_cast<const uint32_t *>(signs + (rotr32(w, (R & 1) ? rot1 : rot0) & 0x3F8u));
+        return (e ^ (one * 0xFFu)) + one;
+    }
+    template <int S>
+    GQ_HD void step(uint32_t (&a)[4]) const {
+        a[0] = quad<2 * S, 0>(); a[1] = quad<2 * S, 1>(); a[2] = quad<2 * S + 1, 0>(); a[3] = quad<2 * S + 1, 1>();
+    }
+    template <int S>
+    GQ_HD void iscale(int &s0, int &s1) const {
+        s0 = (int)(2u * (sw[0][S] >> 28) + 1u);
+        s1 = (int)(2u * (sw[1][S] >> 28) + 1u);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
+};
+
+// the eight scale bytes of a row (a nibble per run of 16) -> 2 s + 1 of the even runs and of the odd runs, one per byte
+GQ_HD inline void iq2_run_scales(uint2 w, uint32_t (&even)[2], uint32_t (&odd)[2]) {
+    even[0] = (w.x & 0x0f0f0f0fu) * 2u + 0x01010101u; even[1] = (w.y & 0x0f0f0f0fu) * 2u + 0x01010101u;
+    odd[0] = ((w.x >> 4) & 0x0f0f0f0fu) * 2u + 0x01010101u; odd[1] = ((w.y >> 4) & 0x0f0f0f0fu) * 2u + 0x01010101u;
+}
+
+template <>
+struct Dec8<GQ_IQ2_XS> {
+    static constexpr int SCHEME = GQ_S16;
+    static constexpr bool A_SIGNED = true;
+    static constexpr int NCORR = 0;
+    uint32_t v[2][8];    // the halfword (9-bit grid index, 7-bit sign index) of run r in half r & 1 of word r >> 1
+    uint32_t sce[2][2], sco[2][2], dd[2];
+    const uint8_t *grid, *signs;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
+        const int t = lane & 3, tp = t >> 1;
+        grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
+        signs = reinterpret_cast<const uint8_t *>(aux.grid + 1024) + 4 * (t & 1);
+        const uint32_t sel = 0x5410u + 0x2222u * (uint32_t)tp;     // halfword tp of each of two words
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint4 w = ld16(slab + 64 * row + 16 * c);        // word j of the row = the two halfwords of run j
+                v[h][2 * c] = prmt(w.x, w.y, sel);
+                v[h][2 * c + 1] = prmt(w.z, w.w, sel);
+            }
+            iq2_run_scales(ld8(slab + 1024 + 8 * row), sce[h], sco[h]);
+            dd[h] = ld2(slab + 1152 + 2 * row);
+        }
+    }
+    template <int R, int H>
+    GQ_HD uint32_t quad() const {
+        const uint32_t w = v[H][R >> 1];
+        const uint32_t goff = (R & 1) ? (w >> 13) & 0xFF8u : (w << 3) & 0xFF8u;
+        const uint32_t soff = (R & 1) ? (w >> 22) & 0x3F8u : (w >> 6) & 0x3F8u;
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + goff);
+        const uint32_t one = *reinterpret_cast<const uint32_t *>(signs + soff);
+        return (e ^ (one * 0xFFu)) + one;
+    }
+    template <int R>
+    GQ_HD void step16(uint32_t (&a)[2]) const { a[0] = quad<R, 0>(); a[1] = quad<R, 1>(); }
+    template <int R>
+    GQ_HD void iscale16(int &s0, int &s1) const {
+        constexpr int ib = R >> 1;
+        s0 = ubyte<(ib & 3)>((R & 1) ? sco[0][ib >> 2] : sce[0][ib >> 2]);
+        s1 = ubyte<(ib & 3)>((R & 1) ? sco[1][ib >> 2] : sce[1][ib >> 2]);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
+};
+
+template <>
+struct Dec8<GQ_IQ2_S> {
+    static constexpr int SCHEME = GQ_S16;
+    static constexpr bool A_SIGNED = true;
+    static constexpr int NCORR = 0;
+    uint32_t q[2][4];    // low grid-index byte of run r in byte r & 3 of word r >> 2
+    uint32_t sg[2][4];   // the lane's sign nibble of run r, same place
+    uint2 qh[2];         // the eight qh bytes per row, shifted so that the lane's pair of bits of run 2 ib + u sits at bit 4 u of byte ib
+    uint32_t sce[2][2], sco[2][2], dd[2];
+    const uint8_t *grid;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
+        const int t = lane & 3, tp = t >> 1, sh = 4 * (t & 1);
+        grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            const uint4 ia = ld16(slab + 32 * row), ib = ld16(slab + 32 * row + 16);
+            q[h][0] = pick_alt_bytes(ia.x, ia.y, tp); q[h][1] = pick_alt_bytes(ia.z, ia.w, tp);
+            q[h][2] = pick_alt_bytes(ib.x, ib.y, tp); q[h][3] = pick_alt_bytes(ib.z, ib.w, tp);
+            const uint4 sa = ld16(slab + 512 + 32 * row), sb = ld16(slab + 512 + 32 * row + 16);
+            sg[h][0] = (pick_alt_bytes(sa.x, sa.y, tp) >> sh) & 0x0f0f0f0fu; sg[h][1] = (pick_alt_bytes(sa.z, sa.w, tp) >> sh) & 0x0f0f0f0fu;
+            sg[h][2] = (pick_alt_bytes(sb.x, sb.y, tp) >> sh) & 0x0f0f0f0fu; sg[h][3] = (pick_alt_bytes(sb.z, sb.w, tp) >> sh) & 0x0f0f0f0fu;
+            uint2 hq = ld8(slab + 1024 + 8 * row);
+            hq.x >>= 2 * tp; hq.y >>= 2 * tp;
+            qh[h] = hq;
+            iq2_run_scales(ld8(slab + 1152 + 8 * row), sce[h], sco[h]);
+            dd[h] = ld2(slab + 1280 + 2 * row);
+        }
+    }
+    template <int R, int H>
+    GQ_HD uint32_t quad() const {
+        constexpr int ib = R >> 1, u = R & 1;
+        const uint32_t idxb = (uint32_t)ubyte<(R & 3)>(q[H][R >> 2]);
+        const uint32_t hw = (ib < 4) ? qh[H].x : qh[H].y;
+        const uint32_t idx = or_and(idxb, shl_c<8 - (8 * (ib & 3) + 4 * u)>(hw), 0x300u);
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + 8 * idx);
+        const uint32_t one = spread_sign((uint32_t)ubyte<(R & 3)>(sg[H][R >> 2]));
+        return (e ^ (one * 0xFFu)) + one;
+    }
+    template <int R>
+    GQ_HD void step16(uint32_t (&a)[2]) const { a[0] = quad<R, 0>(); a[1] = quad<R, 1>(); }
+    template <int R>
+    GQ_HD void iscale16(int &s0, int &s1) const {
+        constexpr int ib = R >> 1;
+        s0 = ubyte<(ib & 3)>((R & 1) ? sco[0][ib >> 2] : sce[0][ib >> 2]);
+        s1 = ubyte<(ib & 3)>((R & 1) ? sco[1][ib >> 2] : sce[1][ib >> 2]);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
+};
+
 }  // namespace gq

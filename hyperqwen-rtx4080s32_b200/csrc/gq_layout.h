@@ -22,7 +22,7 @@
 
 enum GqType {
     GQ_Q4_0 = 2, GQ_Q5_0 = 6, GQ_Q8_0 = 8, GQ_Q2_K = 10, GQ_Q3_K = 11, GQ_Q4_K = 12, GQ_Q5_K = 13,
-    GQ_Q6_K = 14, GQ_IQ3_XXS = 18, GQ_IQ4_NL = 20, GQ_IQ3_S = 21, GQ_IQ4_XS = 23
+    GQ_Q6_K = 14, GQ_IQ2_XXS = 16, GQ_IQ2_XS = 17, GQ_IQ3_XXS = 18, GQ_IQ4_NL = 20, GQ_IQ3_S = 21, GQ_IQ2_S = 22, GQ_IQ4_XS = 23
 };
 
 #ifdef __CUDACC__
@@ -46,6 +46,9 @@ GQ_HD inline int gq_type_bytes(int type) {
         case GQ_IQ3_S: return 110;
         case GQ_IQ4_XS: return 136;
         case GQ_IQ3_XXS: return 98;
+        case GQ_IQ2_XXS: return 66;
+        case GQ_IQ2_XS: return 74;
+        case GQ_IQ2_S: return 82;
         default: return 0;
     }
 }
@@ -63,6 +66,46 @@ GQ_HD inline int gq_type_chunks(int type) {
         default: return 0;
     }
 }
+
+// Codebook types keep a table of grid entries in shared memory while a kernel decodes them.  Kind index of a type
+// (-1: not a codebook type), and the table's bytes in the integer form (form 1: magnitudes as bytes, plus 1 KB of sign
+// words for the types that store 7-bit sign indices) and in the fp16 form (form 0).
+GQ_HD inline int gq_cb_kind(int type) {
+    switch (type) {
+        case GQ_IQ3_S: return 0;
+        case GQ_IQ3_XXS: return 1;
+        case GQ_IQ2_XXS: return 2;
+        case GQ_IQ2_XS: return 3;
+        case GQ_IQ2_S: return 4;
+        default: return -1;
+    }
+}
+#define GQ_CB_KINDS 5
+GQ_HD inline int gq_cb_bytes(int kind, int form) {
+    switch (kind) {
+        case 0: return form ? 2048 : 4096;     // IQ3_S: 512 entries of 4 bytes / of two fp16 pairs
+        case 1: return 2048;                   // IQ3_XXS: 256 entries of 4 bytes + sign words / of two fp16 pairs
+        case 2: return form ? 3072 : 2048;     // IQ2_XXS: 256 entries of 8 bytes (+ sign words)
+        case 3: return form ? 5120 : 4096;     // IQ2_XS: 512 entries of 8 bytes (+ sign words)
+        case 4: return 8192;                   // IQ2_S: 1024 entries of 8 bytes
+        default: return 0;
+    }
+}
+// a kernel whose CTAs decode one type each keeps the CTA's table at the start of a region sized for the largest
+GQ_HD inline int gq_cb_region_max(int mask, int form) {
+    int m = 0;
+    for (int k = 0; k < GQ_CB_KINDS; ++k)
+        if (((mask >> k) & 1) && gq_cb_bytes(k, form) > m) m = gq_cb_bytes(k, form);
+    return m;
+}
+// a kernel whose CTAs may decode two types keeps the tables of all types of the run side by side (fp16 form)
+GQ_HD inline int gq_cb_offset(int mask, int kind) {
+    int o = 0;
+    for (int k = 0; k < kind; ++k)
+        if ((mask >> k) & 1) o += gq_cb_bytes(k, 0);
+    return o;
+}
+GQ_HD inline int gq_cb_region_sum(int mask) { return gq_cb_offset(mask, GQ_CB_KINDS); }
 
 // Source of packed byte p (0 <= p < 16 * bytes_per_256) of a slab: *row in 0..15, *byte = offset inside
 // that row's 256-weight segment of raw GGUF bytes.  Returns 0, or -1 for a bad argument.
@@ -147,6 +190,23 @@ GQ_HD inline int gq_slab_src(int type, int p, int *row, int *byte) {
             q -= 128;
             if (q < 64) { *row = q >> 2; *byte = 106 + (q & 3); return 0; }
             q -= 64;
+            *row = q >> 1; *byte = q & 1; return 0;
+        case GQ_IQ2_XXS:                           // no lane-ordered chunks (two lanes share a grid entry): per row the eight
+                                                   // index words (32 B), then per row the eight sign-and-scale words, then d
+            if (q < 1024) { const int j = q & 31; *row = (q >> 5) & 15; *byte = 2 + 8 * (j >> 2) + 4 * (q >> 9) + (j & 3); return 0; }
+            q -= 1024;
+            *row = q >> 1; *byte = q & 1; return 0;
+        case GQ_IQ2_XS:                            // per row the 32 index-and-sign halfwords (64 B), then scales[8], then d
+            if (q < 1024) { *row = q >> 6; *byte = 2 + (q & 63); return 0; }
+            q -= 1024;
+            if (q < 128) { *row = q >> 3; *byte = 66 + (q & 7); return 0; }
+            q -= 128;
+            *row = q >> 1; *byte = q & 1; return 0;
+        case GQ_IQ2_S:                             // per row 32 index bytes, then per row 32 sign bytes, qh[8], scales[8], d
+            if (q < 1024) { *row = (q >> 5) & 15; *byte = 2 + 32 * (q >> 9) + (q & 31); return 0; }
+            q -= 1024;
+            if (q < 256) { *row = (q >> 3) & 15; *byte = 66 + 8 * (q >> 7) + (q & 7); return 0; }
+            q -= 256;
             *row = q >> 1; *byte = q & 1; return 0;
         case GQ_IQ3_XXS:                           // the eight sign-and-scale words per row (32 B), then d per row
             if (q < 512) { *row = q >> 5; *byte = 66 + (q & 31); return 0; }

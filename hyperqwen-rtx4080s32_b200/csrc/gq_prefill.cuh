@@ -21,7 +21,7 @@
 #pragma once
 #include "gq_decode.cuh"
 
-// (included after the two __constant__ format tables c_iq3s_grid / c_iq3xxs_grid / c_iq4_kvalues are declared)
+// (included after the two __constant__ format tables c_iq3s_grid / c_iq3xxs_grid / c_iq2*_grid / c_iq4_kvalues are declared)
 namespace gq {
 
 #define GQ_PF_STAGES 4
@@ -42,6 +42,7 @@ struct PrefillParams {
     int split;                // split-K factor (grid.z); > 1: fp32 partials instead of y
     float *partials;          // [split][M][n_total]
     int64_t n_total;
+    int cb_mask;              // the codebook types of the run (bit gq_cb_kind): their tables sit side by side in shared memory
 };
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -150,7 +151,7 @@ __device__ __forceinline__ bool pf_idle(int nb, uint64_t *a_full, uint64_t *free
 template <int NB, bool SPLITK>
 __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_kernel(const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // layout: [stages x (A 16 KB | B NB*128)] [barriers] [tmem slot] [IQ3_S and IQ3_XXS grids 6 KB]
+    // layout: [stages x (A 16 KB | B NB*128)] [barriers] [tmem slot] [codebook tables of the run's types]
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int B_BYTES = NB * 128;
     constexpr int STAGE = GQ_PF_A_BYTES + B_BYTES;
@@ -171,6 +172,14 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
     const bool has1 = 2 * pair + 1 < p.n_desc;
     const int32_t *d1 = has1 ? d0 + GQ_DESC_WORDS : d0;
 
+    // a codebook type the call's run_info did not announce has no table space: report and leave (nothing is allocated yet)
+    {
+        const int k0 = gq_cb_kind(d0[1]), k1 = gq_cb_kind(d1[1]);
+        if ((k0 >= 0 && !((p.cb_mask >> k0) & 1)) || (k1 >= 0 && !((p.cb_mask >> k1) & 1))) {
+            if (threadIdx.x == 0) { pdl_wait(); report_status(p.status, GQ_DEV_BAD_SHAPE); }      // after the preparation kernel has cleared the word
+            return;
+        }
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < GQ_PF_STAGES; ++s) {
             mbar_init(a_full + s, GQ_PF_DEQ_WARPS);
@@ -180,11 +189,20 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
         mbar_init(done, 1);
         fence_barrier_init();
     }
-    if (d0[1] == GQ_IQ3_S || d1[1] == GQ_IQ3_S) {
-        for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]);
-    }
-    if (d0[1] == GQ_IQ3_XXS || d1[1] == GQ_IQ3_XXS) {
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_s[GQ_IQ3XXS_GRID_OFFSET + i] = iq3s_grid_entry(c_iq3xxs_grid[i]);
+    // the codebook tables of the two tiles' types, each at its place among the tables of the run's types
+    for (int which = 0; which < 2; ++which) {
+        const int ty = which ? d1[1] : d0[1], kind = gq_cb_kind(ty);
+        if (kind < 0 || (which && d1[1] == d0[1])) continue;
+        uint8_t *tb = reinterpret_cast<uint8_t *>(grid_s) + gq_cb_offset(p.cb_mask, kind);
+        uint32_t *t32 = reinterpret_cast<uint32_t *>(tb);
+        uint2 *t64 = reinterpret_cast<uint2 *>(tb);
+        switch (ty) {
+            case GQ_IQ3_S: for (int i = threadIdx.x; i < 512; i += blockDim.x) t64[i] = iq3s_grid_entry(c_iq3s_grid[i]); break;
+            case GQ_IQ3_XXS: for (int i = threadIdx.x; i < 256; i += blockDim.x) t64[i] = iq3s_grid_entry(c_iq3xxs_grid[i]); break;
+            case GQ_IQ2_XXS: for (int i = threadIdx.x; i < 512; i += blockDim.x) t32[i] = prmt(c_iq2xxs_grid[i], 0u, 0x3120u); break;
+            case GQ_IQ2_XS: for (int i = threadIdx.x; i < 1024; i += blockDim.x) t32[i] = prmt(c_iq2xs_grid[i], 0u, 0x3120u); break;
+            case GQ_IQ2_S: for (int i = threadIdx.x; i < 2048; i += blockDim.x) t32[i] = prmt(c_iq2s_grid[i], 0u, 0x3120u); break;
+        }
     }
     if (!has1) {
         // rows 64..127 of every A stage are never written: clear them once
@@ -234,7 +252,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
         const int slab = warp - 2;                 // 0..7: rows 16*slab .. 16*slab+15 of the 128
         const int32_t *dd = (slab < 4) ? d0 : d1;
         DecAux aux;
-        aux.grid = grid_s;
+        aux.grid = reinterpret_cast<const uint2 *>(reinterpret_cast<const uint8_t *>(grid_s) + (gq_cb_kind(dd[1]) >= 0 ? gq_cb_offset(p.cb_mask, gq_cb_kind(dd[1])) : 0));
         {
             uint32_t tb[4];
 #pragma unroll
@@ -254,6 +272,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
             switch (dd[1]) {
                 GQ_PF(GQ_Q4_0) GQ_PF(GQ_Q5_0) GQ_PF(GQ_Q8_0) GQ_PF(GQ_Q2_K) GQ_PF(GQ_Q3_K) GQ_PF(GQ_Q4_K)
                 GQ_PF(GQ_Q5_K) GQ_PF(GQ_Q6_K) GQ_PF(GQ_IQ4_NL) GQ_PF(GQ_IQ3_S) GQ_PF(GQ_IQ4_XS) GQ_PF(GQ_IQ3_XXS)
+                GQ_PF(GQ_IQ2_XXS) GQ_PF(GQ_IQ2_XS) GQ_PF(GQ_IQ2_S)
             }
 #undef GQ_PF
         }

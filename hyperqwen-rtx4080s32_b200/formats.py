@@ -19,7 +19,8 @@ IQ4_NL, IQ3_S, IQ4_XS = 20, 21, 23
 IQ2_XXS, IQ2_XS, IQ3_XXS, IQ2_S = 16, 17, 18, 22
 
 TYPE_NAMES = {Q4_0: "Q4_0", Q5_0: "Q5_0", Q8_0: "Q8_0", Q2_K: "Q2_K", Q3_K: "Q3_K", Q4_K: "Q4_K", Q5_K: "Q5_K",
-              Q6_K: "Q6_K", IQ4_NL: "IQ4_NL", IQ3_S: "IQ3_S", IQ4_XS: "IQ4_XS", IQ3_XXS: "IQ3_XXS"}
+              Q6_K: "Q6_K", IQ4_NL: "IQ4_NL", IQ3_S: "IQ3_S", IQ4_XS: "IQ4_XS", IQ3_XXS: "IQ3_XXS", IQ2_XXS: "IQ2_XXS",
+              IQ2_XS: "IQ2_XS", IQ2_S: "IQ2_S"}
 TYPE_IDS = {v: k for k, v in TYPE_NAMES.items()}
 SUPPORTED_TYPES = frozenset(TYPE_NAMES)
 NORTH_STAR_TYPES = frozenset({Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ3_S, IQ4_XS})

@@ -275,6 +275,47 @@ def _enc_iq3_xxs(w):
     return np.concatenate([dbytes.reshape(n, 2), idx.astype(np.uint8), word.astype("<u4").view(np.uint8).reshape(n, 32)], axis=1)
 
 
+def _enc_iq2(w, wtype):
+    """IQ2_XXS / IQ2_XS / IQ2_S: weight = d (2 s + 1) / 8 x magnitude x sign, eight magnitudes per grid index; the scale
+    is per 32 weights (IQ2_XXS) or per 16; IQ2_XXS and IQ2_XS store seven sign bits per group of eight
+    (gguf-plugin/gluon/iq2.py:6-23)."""
+    import gguf.quants as gq
+
+    cls = {F.IQ2_XXS: gq.IQ2_XXS, F.IQ2_XS: gq.IQ2_XS, F.IQ2_S: gq.IQ2_S}[wtype]
+    cls.init_grid()
+    grid = cls.grid.reshape(-1, 8).astype(np.float32)
+    n = w.shape[0]
+    grp = 32 if wtype == F.IQ2_XXS else 16
+    wb = w.reshape(n, 256 // grp, grp)
+    step_t = np.abs(wb).max(-1) / 36.0
+    d, dbytes = _f16(step_t.max(-1, keepdims=True) * 8.0 / 31.0)
+    s = np.clip(np.rint((_safe_div(step_t * 8.0, d) - 1.0) / 2.0), 0, 15).astype(np.uint32)
+    step = np.broadcast_to((d * (2 * s.astype(np.float32) + 1) / 8.0)[..., None], wb.shape)
+    idx = _nearest_grid(_safe_div(np.abs(wb), step).reshape(n * 32, 8), grid).reshape(n, 32).astype(np.uint32)
+    w8 = w.reshape(n * 32, 8)
+    if wtype == F.IQ2_S:
+        neg = w8 < 0
+        signs = np.zeros(n * 32, np.uint8)
+        for j in range(8):
+            signs |= neg[:, j].astype(np.uint8) << j
+        signs = signs.reshape(n, 32)
+        qh = np.zeros((n, 8), np.uint8)
+        for l in range(4):
+            qh |= ((idx[:, l::4] >> 8) & 3).astype(np.uint8) << (2 * l)
+        sc = (s[:, 0::2] | (s[:, 1::2] << 4)).astype(np.uint8)
+        return np.concatenate([dbytes.reshape(n, 2), (idx & 0xFF).astype(np.uint8), signs, qh, sc], axis=1)
+    signs = (_even_signs(w8) & 0x7F).astype(np.uint32).reshape(n, 32)
+    if wtype == F.IQ2_XS:
+        qs = (idx | (signs << 9)).astype("<u2").view(np.uint8).reshape(n, 64)
+        sc = (s[:, 0::2] | (s[:, 1::2] << 4)).astype(np.uint8)
+        return np.concatenate([dbytes.reshape(n, 2), qs, sc], axis=1)
+    i4, s4 = idx.reshape(n, 8, 4), signs.reshape(n, 8, 4)
+    lo = i4[..., 0] | (i4[..., 1] << 8) | (i4[..., 2] << 16) | (i4[..., 3] << 24)
+    hi = s4[..., 0] | (s4[..., 1] << 7) | (s4[..., 2] << 14) | (s4[..., 3] << 21) | (s << 28)
+    qs = np.stack([lo, hi], axis=-1).astype("<u4").view(np.uint8).reshape(n, 64)
+    return np.concatenate([dbytes.reshape(n, 2), qs], axis=1)
+
+
 def _enc_gguf(wtype):
     def enc(w):
         from gguf.constants import GGMLQuantizationType
@@ -286,6 +327,7 @@ def _enc_gguf(wtype):
 
 _ENCODERS = {F.Q4_K: _enc_q4_k, F.Q5_K: _enc_q5_k, F.Q2_K: _enc_q2_k, F.Q3_K: _enc_q3_k, F.Q6_K: _enc_q6_k,
              F.IQ4_NL: _enc_iq4_nl, F.IQ4_XS: _enc_iq4_xs, F.IQ3_S: _enc_iq3_s, F.IQ3_XXS: _enc_iq3_xxs,
+             F.IQ2_XXS: lambda w: _enc_iq2(w, F.IQ2_XXS), F.IQ2_XS: lambda w: _enc_iq2(w, F.IQ2_XS), F.IQ2_S: lambda w: _enc_iq2(w, F.IQ2_S),
              F.Q8_0: _enc_gguf(F.Q8_0), F.Q4_0: _enc_gguf(F.Q4_0), F.Q5_0: _enc_gguf(F.Q5_0)}
 
 

@@ -278,6 +278,10 @@ static void deq_iq4_xs(const uint8_t *b, float *y) {
     }
 }
 
+/* sign factors, read from memory so that the product stays a multiplication (a negation would flip the sign of a NaN,
+ * which the multiplication gguf-py performs leaves alone) */
+static const volatile float g_sign[2] = {1.0f, -1.0f};
+
 /* The 8-bit sign mask of a group of 8 weights from its stored 7-bit index: bit 7 is the parity of the seven
  * (llama.cpp's ksigns_iq2xs table, stated as arithmetic: gguf-plugin/gluon/iq2.py:27-28). */
 static int sign_mask8(int idx7) {
@@ -299,7 +303,7 @@ static void deq_iq3_xxs(const uint8_t *b, float *y) {
             int sg = sign_mask8((int)((w >> (7 * l)) & 0x7F));
             for (int j = 0; j < 8; j++) {
                 int mag = g_iq3xxs_grid[qs[8 * ib + 2 * l + (j >> 2)]][j & 3];
-                y[32 * ib + 8 * l + j] = (db * (float)mag) * (((sg >> j) & 1) ? -1.0f : 1.0f);
+                y[32 * ib + 8 * l + j] = (db * (float)mag) * g_sign[(sg >> j) & 1];
             }
         }
     }
@@ -316,7 +320,7 @@ static void deq_iq2_xxs(const uint8_t *b, float *y) {
         for (int l = 0; l < 4; l++) {
             int sg = sign_mask8((int)((w >> (7 * l)) & 0x7F));
             for (int j = 0; j < 8; j++)
-                y[32 * ib + 8 * l + j] = (db * (float)g_iq2xxs_grid[q[l]][j]) * (((sg >> j) & 1) ? -1.0f : 1.0f);
+                y[32 * ib + 8 * l + j] = (db * (float)g_iq2xxs_grid[q[l]][j]) * g_sign[(sg >> j) & 1];
         }
     }
 }
@@ -332,7 +336,7 @@ static void deq_iq2_xs(const uint8_t *b, float *y) {
         float db = d * (0.5f + (float)s) * 0.25f;
         int sg = sign_mask8(v >> 9);
         for (int j = 0; j < 8; j++)
-            y[8 * g + j] = (db * (float)g_iq2xs_grid[v & 511][j]) * (((sg >> j) & 1) ? -1.0f : 1.0f);
+            y[8 * g + j] = (db * (float)g_iq2xs_grid[v & 511][j]) * g_sign[(sg >> j) & 1];
     }
 }
 
@@ -346,7 +350,7 @@ static void deq_iq2_s(const uint8_t *b, float *y) {
         int s = (sc[g >> 2] >> (4 * ((g >> 1) & 1))) & 0xF;
         float db = d * (0.5f + (float)s) * 0.25f;
         for (int j = 0; j < 8; j++)
-            y[8 * g + j] = (db * (float)g_iq2s_grid[idx][j]) * (((signs[g] >> j) & 1) ? -1.0f : 1.0f);
+            y[8 * g + j] = (db * (float)g_iq2s_grid[idx][j]) * g_sign[(signs[g] >> j) & 1];
     }
 }
 

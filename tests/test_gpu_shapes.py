@@ -222,3 +222,22 @@ def test_extreme_block_scales(t, d_exp):
         assert torch.isfinite(y).all()
         err = oracle.rel_err(y.float().cpu().numpy(), oracle.matmul_f64(x.float().cpu().numpy(), raw.numpy(), t))
         assert err < TOL_TIGHT, f"{F.TYPE_NAMES[t]} d=2^{d_exp} M={m}: {err:.3e}"
+
+
+@pytest.mark.parametrize("t", [F.IQ2_S, F.IQ3_S])
+def test_a_codebook_type_the_run_info_does_not_announce_is_reported_not_run(t):
+    """The kernels keep a codebook type's grid in shared memory sized from run_info.  A caller whose run_info leaves the
+    type out gets device status 2 and an unusable result, on both paths; nothing is read or written out of bounds."""
+    n_out, k = 128, 512
+    raw = synth.random_blocks(n_out, k, t, seed=77, device=dev())
+    tiles = ops.repack_tiles(raw, n_out, t).reshape(-1)
+    d1 = torch.from_numpy(ops.build_descs([t], [n_out], k, 1)).to(dev())
+    assert ops.device_status() == 0
+    ops.grouped_gemm(synth.activations(4, k, device=dev()), tiles, d1, 1, [F.Q8_0, F.Q4_K], n_out)      # large enough stages, no table
+    assert ops.device_status() == 2
+    ops.grouped_gemm(synth.activations(4, k, device=dev()), tiles, d1, 1, [F.Q4_K], n_out)              # a single type that is not the tiles'
+    assert ops.device_status() == 2
+    ops.prefill_gemm(synth.activations(128, k, device=dev()), tiles, d1, n_out, wtypes=[F.Q8_0])
+    assert ops.device_status() == 2
+    y = ops.grouped_gemm(synth.activations(4, k, device=dev()), tiles, d1, 1, [t], n_out)
+    assert ops.device_status() == 0 and not torch.isnan(y).any()

@@ -31,7 +31,7 @@ def test_slab_map_is_a_permutation(gq_lib, t):
     assert gq_lib.gq_bytes_per_256(t) == bb
     assert m.shape == (16 * bb,) and sorted(m.tolist()) == list(range(16 * bb))
     # lane-ordered chunks: the 16 bytes of lane l in any chunk come from rows g and g+8 only (g = l // 4)
-    chunks = {2: 4, 6: 4, 8: 8, 10: 2, 11: 3, 12: 4, 13: 5, 14: 6, 18: 2, 20: 4, 21: 2, 23: 4}[t]
+    chunks = {2: 4, 6: 4, 8: 8, 10: 2, 11: 3, 12: 4, 13: 5, 14: 6, 16: 0, 17: 0, 18: 2, 20: 4, 21: 2, 22: 0, 23: 4}[t]
     rows = (m[:512 * chunks] // bb).reshape(chunks, 32, 16)
     for l in range(32):
         assert set(np.unique(rows[:, l])) <= {l // 4, l // 4 + 8}
@@ -43,7 +43,8 @@ def test_packed_bytes_and_errors(gq_lib):
     assert gq_lib.gq_packed_bytes(99, 70, 768) == -1
     assert gq_lib.gq_packed_bytes(F.Q4_K, 70, 700) == -2
     assert gq_lib.gq_bytes_per_256(99) == 0
-    assert gq_lib.gq_run_info(2, (ctypes.c_int32 * 2)(F.Q4_K, F.IQ3_S)) == 144 | (1 << 16)
+    assert gq_lib.gq_run_info(2, (ctypes.c_int32 * 2)(F.Q4_K, F.IQ3_S)) == 144 | (1 << 16) | (1 << 22)      # a codebook type: flag, and its kind bit
+    assert gq_lib.gq_run_info(1, (ctypes.c_int32 * 1)(F.IQ2_S)) == 82 | (1 << 16) | (F.IQ2_S << 17) | (1 << 26)  # one type: its id in bits 17..21
     assert gq_lib.gq_run_info(1, (ctypes.c_int32 * 1)(5)) == -1
 
 
