@@ -537,6 +537,7 @@ def run_ours(args):
 # ---- per-type sweeps (the per-type decode sweep of BASELINE configs[1] and the prefill sweep of configs[2]) ----------
 #   python bench.py --sweep decode --types Q4_K Q6_K --shapes gate kv --m 1 8 [--split 1 2] [--eager --iters 3]
 #   python bench.py --sweep prefill --types Q4_K --shapes gate_up down --m 512 2048 8192
+#   python bench.py --sweep neighbours --sweep-m 1 8      (silu_and_mul / add + RMSNorm folded into the layer behind them)
 # Decode: for each type x shape x batch the grouped kernel alone (activations prepared beforehand) and the whole call
 # (prepare + kernel + partial sum) as CUDA-graph replays over distinct weight copies totalling more than the L2, median of
 # 7 — the reference's timing method (gguf-plugin/test_gluon_kq_gpu.py:198-245) —, microseconds and GB/s of raw GGUF block
@@ -605,6 +606,37 @@ def sweep_prefill(a, dev) -> None:
 
 
 
+def sweep_neighbours(a, dev) -> None:
+    """The ops either side of a linear at decode batch sizes: down_proj with silu_and_mul in front and gate_up_proj with
+    add + RMSNorm in front, as separate torch operations and folded into the layer's activation preparation; microseconds
+    per layer, CUDA-graph replay over 24 layers of distinct Q4_K weights (more than the L2)."""
+    from hyperqwen_rtx4080s32_b200 import linear
+
+    k, n, layers = 17408, 5120, 24
+    downs, gate_ups = [], []
+    for i in range(layers):
+        lin = linear.GGUFLinear(k, [n])
+        lin.load_shard(synth.random_blocks(n, k, F.Q4_K, seed=i, device=dev), F.Q4_K)
+        downs.append(lin.finalize())
+        lin = linear.GGUFLinear(n, [k, k])
+        for j in range(2):
+            lin.load_shard(synth.random_blocks(k, n, F.Q4_K, seed=100 + 2 * i + j, device=dev), F.Q4_K, j)
+        gate_ups.append(lin.finalize())
+    w = torch.ones(n, dtype=torch.bfloat16, device=dev)
+    for m in a.m:
+        gu = synth.activations(m, 2 * k, device=dev)
+        x, res = synth.activations(m, n, device=dev), synth.activations(m, n, seed=5, device=dev)
+        pre = ops.PreAddRMSNorm(w, 1e-6, residual=res)
+        cases = (("down alone", lambda: [l(gu[:, :k]) for l in downs]),
+                 ("silu_and_mul (torch) + down", lambda: [l(torch.nn.functional.silu(gu[:, :k]) * gu[:, k:]) for l in downs]),
+                 ("down, silu_and_mul folded", lambda: [l(gu, pre=ops.PreSiluMul()) for l in downs]),
+                 ("gate_up alone", lambda: [l(x) for l in gate_ups]),
+                 ("add + RMSNorm (torch) + gate_up", lambda: [l(pre.unfused(x)) for l in gate_ups]),
+                 ("gate_up, add + RMSNorm folded", lambda: [l(x, pre=pre) for l in gate_ups]))
+        for name, fn in cases:
+            _say(f"M={m:2} {name:32}: {1e3 * _graph_time(fn, layers):7.2f} us per layer", flush=True)
+
+
 def run_sweep(a) -> None:
     import numpy as np  # noqa: F401
     import torch
@@ -613,12 +645,14 @@ def run_sweep(a) -> None:
 
     globals().update(np=np, torch=torch, _lib=_lib, F=F, ops=ops, synth=synth)
     a.types = a.types or list(F.TYPE_IDS)
-    a.m = a.sweep_m or ([1, 8] if a.sweep == "decode" else [512, 2048, 8192])
+    a.m = a.sweep_m or ([512, 2048, 8192] if a.sweep == "prefill" else [1, 8])
     a.shapes = a.shapes or (["q", "kv", "gate", "down"] if a.sweep == "decode" else ["gate_up", "down"])
     dev = torch.device("cuda", 0)
     L = _lib.lib()
     if a.sweep == "prefill":
         return sweep_prefill(a, dev)
+    if a.sweep == "neighbours":
+        return sweep_neighbours(a, dev)
     for tn in a.types:
         t = F.TYPE_IDS[tn]
         for sn in a.shapes:
@@ -687,7 +721,7 @@ def main():
     ap.add_argument("--no-m-sweep", action="store_true", help="skip the other batch sizes of the config (M = 1, 4, 64; tensor parallel: 1, 64, 4096)")
     ap.add_argument("--unfused-allreduce", action="store_true", help="tensor parallel: all-reduce with the library's separate push kernel instead of inside the grouped kernel")
     ap.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: use NCCL for the row-parallel all-reduce instead of the library's push kernel")
-    ap.add_argument("--sweep", choices=["decode", "prefill"], help="per-type sweep instead of the benchmark line (prints a table)")
+    ap.add_argument("--sweep", choices=["decode", "prefill", "neighbours"], help="per-type sweep instead of the benchmark line (prints a table)")
     ap.add_argument("--types", nargs="*", default=[], help="--sweep: GGML type names (default all)")
     ap.add_argument("--shapes", nargs="*", default=[], help="--sweep: q kv o gate down (decode; or NxK), gate_up down q (prefill)")
     ap.add_argument("--sweep-m", nargs="*", type=int, default=[], help="--sweep: batch sizes")

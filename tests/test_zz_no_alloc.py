@@ -51,6 +51,7 @@ def test_static_workspace_entry_point_matches_twice_in_a_row():
         y, y_ref = _call_both(x, packed, desc, split, wts, n_total)
         assert not torch.isnan(y).any()
         assert torch.equal(y, y_ref)
+        assert ops.device_status() == 0      # the entry point has no workspace to read a status word from: the device's word
 
 
 def test_static_workspace_entry_point_rejects_oversized_calls():
