@@ -120,9 +120,11 @@ __global__ void __launch_bounds__(256) unrepack_kernel(int type, int B, const ui
 // bit-exact dequantiser (fp32 in the format reference's operation order: (d*sc) first, then *q, then -(dmin*m);
 // explicit round-to-nearest multiplies and subtracts so nothing is fused)
 // ---------------------------------------------------------------------------------------------------
-__constant__ uint32_t c_iq3s_grid[512];
-__constant__ uint32_t c_iq3xxs_grid[256];
-__constant__ uint32_t c_iq2xxs_grid[512], c_iq2xs_grid[1024], c_iq2s_grid[2048];    // two words per entry
+// The codebook grids live in global memory, not in constant memory: the kernels copy them into shared memory with one
+// index per thread, which the constant cache would serve one address at a time.
+__device__ uint32_t c_iq3s_grid[512];
+__device__ uint32_t c_iq3xxs_grid[256];
+__device__ uint32_t c_iq2xxs_grid[512], c_iq2xs_grid[1024], c_iq2s_grid[2048];    // two words per entry
 __constant__ int8_t c_iq4_kvalues[16];
 
 // A bounded wait that runs out is reported twice: in the status word of the launch's workspace (gq_read_status) and in
@@ -701,15 +703,18 @@ struct Ring {
     uint8_t *smem;
     uint64_t *full, *empty;
     int stages, stage_bytes, wmax, nk;
+    const uint32_t *ar_counter;      // fused all-reduce: this warp's call counter (null: none), read early into ar_prev
 };
 
 // the consumer loop of one warp for a CTA whose shard is of TYPE: waits for each stage, processes its slab,
 // releases the stage.  Returns false if a bounded wait ran out.
 template <int TYPE, int MT>
-__device__ __forceinline__ bool consume(const Ring &r, int slab_off, const DecAux &aux, int lane, float (&acc)[MT][4]) {
+__device__ __forceinline__ bool consume(const Ring &r, int slab_off, const DecAux &aux, int lane, float (&acc)[MT][4], uint32_t &ar_prev) {
     float z[4] = {0.f, 0.f, 0.f, 0.f};
     for (int i = 0, s = 0, round = 0; i < r.nk; ++i) {
         if (!mbar_wait(r.full + s, round & 1)) return false;
+        // the first stage holds activations, so every launch in front of this one has finished and the counter is final
+        if (i == 0 && r.ar_counter && lane == 0) ar_prev = *reinterpret_cast<const volatile uint32_t *>(r.ar_counter);
         const uint8_t *st = r.smem + (size_t)s * r.stage_bytes;
         slab_kblock<TYPE, MT>(st + slab_off, st + r.wmax, aux, lane, acc, z);
         __syncwarp();
@@ -882,9 +887,10 @@ __device__ __forceinline__ void slab_kblock8(const uint8_t *slab, const uint8_t 
 
 
 template <int TYPE, int MT>
-__device__ __forceinline__ bool consume8(const Ring &r, int xs_off, int slab_off, const DecAux8 &aux, int lane, float (&acc)[MT][4]) {
+__device__ __forceinline__ bool consume8(const Ring &r, int xs_off, int slab_off, const DecAux8 &aux, int lane, float (&acc)[MT][4], uint32_t &ar_prev) {
     for (int i = 0, s = 0, round = 0; i < r.nk; ++i) {
         if (!mbar_wait(r.full + s, round & 1)) return false;
+        if (i == 0 && r.ar_counter && lane == 0) ar_prev = *reinterpret_cast<const volatile uint32_t *>(r.ar_counter);
         const uint8_t *st = r.smem + (size_t)s * r.stage_bytes;
         slab_kblock8<TYPE, MT>(st + slab_off, st + r.wmax, xs_off, aux, lane, acc);
         __syncwarp();
@@ -904,11 +910,10 @@ __device__ __forceinline__ bool consume8(const Ring &r, int xs_off, int slab_off
 // microseconds per warp).  No loads from remote memory, no multicast.  The call number lives in device memory per
 // (tile, warp) and selects one of two slot sets; a stale word of the same set carries an older number, and a rank
 // cannot run two calls ahead of a peer because each call needs every peer's words of that call.
-__device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const uint32_t *blk, int unit, int col, int ncols, int lane) {
+__device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const uint32_t *blk, int unit, int col, int ncols, int lane, uint32_t prev) {
     const ArFused &a = p.ar;
-    uint32_t seq = 0;
-    if (lane == 0) seq = a.counters[unit] + 1;
-    seq = __shfl_sync(0xffffffffu, seq, 0);
+    // the call number: one more than the counter, which lane 0 read while the first k-block was being multiplied
+    const uint32_t seq = __shfl_sync(0xffffffffu, prev, 0) + 1;
     const uint32_t set = seq & 1u;
     const int M = p.M, half = ncols >> 1;
     const int64_t row_words = p.n_total >> 1, slot_words = a.slot_bytes >> 3;
@@ -925,30 +930,51 @@ __device__ __noinline__ void fused_allreduce_block(const GemvParams &p, const ui
     const unsigned long long *src = reinterpret_cast<const unsigned long long *>(a.buf[a.rank]) + (int64_t)set * a.world * slot_words + first;
     bool fail = false;
     uint64_t t0 = 0;
-    for (int e = lane; e < n_el; e += 32) {
-        const int n = e / half, c2 = e - n * half;
-        float s0 = 0.f, s1 = 0.f;
-        for (int r = 0; r < a.world; ++r) {
-            const unsigned long long *q = src + (int64_t)r * slot_words + n * row_words + c2;
-            unsigned long long w;
-            for (uint32_t it = 0;; ++it) {
-                asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(q) : "memory");
-                if ((uint32_t)(w >> 32) == seq) break;
-                if ((it & 255u) == 255u) {      // the clock is read only once a wait has become long
-                    const uint64_t now = global_timer_ns();
-                    if (t0 == 0) t0 = now;
-                    if (now - t0 > a.wait_ns) { fail = true; break; }
-                }
+    // Two elements per lane and pass; the words of all ranks for both are requested before any is looked at, so a pass
+    // costs one trip to the L2 whatever the number of ranks (polled one after the other, the 2 x 8 dependent loads of an
+    // 8-rank exchange took longer than the kernel in front of them).
+    for (int e0 = lane; e0 < n_el; e0 += 64) {
+        const int e1 = e0 + 32;
+        const bool has1 = e1 < n_el;
+        const int n0 = e0 / half, c0 = e0 - n0 * half, n1 = has1 ? e1 / half : n0, c1 = has1 ? e1 - n1 * half : c0;
+        const unsigned long long *q0 = src + n0 * row_words + c0, *q1 = src + n1 * row_words + c1;
+        unsigned long long w0[GQ_AR_MAX_WORLD], w1[GQ_AR_MAX_WORLD];
+        const uint32_t all = (1u << a.world) - 1u;
+        uint32_t pending = all | (has1 ? all << 8 : 0u);
+        for (uint32_t it = 0; pending; ++it) {
+#pragma unroll
+            for (int r = 0; r < GQ_AR_MAX_WORLD; ++r) {
+                if ((pending >> r) & 1u) asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w0[r]) : "l"(q0 + (int64_t)r * slot_words) : "memory");
+                if ((pending >> (8 + r)) & 1u) asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w1[r]) : "l"(q1 + (int64_t)r * slot_words) : "memory");
             }
-            if (fail) break;
-            const uint32_t v = (uint32_t)w;
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v));
-            s0 += f.x; s1 += f.y;
+#pragma unroll
+            for (int r = 0; r < GQ_AR_MAX_WORLD; ++r) {
+                if (((pending >> r) & 1u) && (uint32_t)(w0[r] >> 32) == seq) pending &= ~(1u << r);
+                if (((pending >> (8 + r)) & 1u) && (uint32_t)(w1[r] >> 32) == seq) pending &= ~(1u << (8 + r));
+            }
+            if (pending && (it & 255u) == 255u) {      // the clock is read only once a wait has become long
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > a.wait_ns) { fail = true; break; }
+            }
         }
         if (fail) break;
-        __nv_bfloat16 *yp = p.y + (int64_t)n * p.ldy + col + 2 * c2;
-        if (!(reinterpret_cast<uintptr_t>(yp) & 3)) *reinterpret_cast<__nv_bfloat162 *>(yp) = __floats2bfloat162_rn(s0, s1);
-        else { yp[0] = __float2bfloat16_rn(s0); yp[1] = __float2bfloat16_rn(s1); }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            if (k == 1 && !has1) break;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int r = 0; r < GQ_AR_MAX_WORLD; ++r) {
+                if (r < a.world) {
+                    const uint32_t v = (uint32_t)(k ? w1[r] : w0[r]);
+                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v));
+                    s0 += f.x; s1 += f.y;
+                }
+            }
+            __nv_bfloat16 *yp = p.y + (int64_t)(k ? n1 : n0) * p.ldy + col + 2 * (k ? c1 : c0);
+            if (!(reinterpret_cast<uintptr_t>(yp) & 3)) *reinterpret_cast<__nv_bfloat162 *>(yp) = __floats2bfloat162_rn(s0, s1);
+            else { yp[0] = __float2bfloat16_rn(s0); yp[1] = __float2bfloat16_rn(s1); }
+        }
     }
     fail = __any_sync(0xffffffffu, fail);
     if (lane == 0) {
@@ -1003,6 +1029,8 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     Ring ring;
     ring.smem = smem; ring.full = full; ring.empty = empty;
     ring.stages = stages; ring.stage_bytes = stage_bytes; ring.wmax = wmax; ring.nk = nk;
+    ring.ar_counter = (p.ar.world > 0 && (p.split == 1 || p.cluster) && split_idx == 0 && warp < GQ_CONSUMER_WARPS)
+                          ? p.ar.counters + (int64_t)(blockIdx.x / (unsigned)p.split) * GQ_CONSUMER_WARPS + warp : nullptr;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, GQ_CONSUMER_WARPS); }
@@ -1088,6 +1116,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
     for (int nt = 0; nt < MT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
     bool ok = true;
+    uint32_t ar_prev = 0;
     const int slab_off = warp * 16 * B;
     // the IQ4 codebook in four registers: signed bytes for the integer form, + 128 for the fp16 form
     Iq4Table iq4;
@@ -1106,9 +1135,9 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         aux.grid = reinterpret_cast<const uint32_t *>(grid_s);
         aux.iq4 = iq4;
         const int xs_off = M * GQ_X8_ROW;
-#define GQ_CONSUME(T) case T: ok = consume8<T, MT>(ring, xs_off, slab_off, aux, lane, acc); break;
+#define GQ_CONSUME(T) case T: ok = consume8<T, MT>(ring, xs_off, slab_off, aux, lane, acc, ar_prev); break;
         if constexpr (ONLY != 0) {
-            ok = consume8<(ONLY ? ONLY : GQ_Q4_K), MT>(ring, xs_off, slab_off, aux, lane, acc);
+            ok = consume8<(ONLY ? ONLY : GQ_Q4_K), MT>(ring, xs_off, slab_off, aux, lane, acc, ar_prev);
         } else {
             switch (type) {
                 GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
@@ -1121,7 +1150,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         DecAux aux;
         aux.grid = grid_s;
         aux.iq4 = iq4;
-#define GQ_CONSUME(T) case T: ok = consume<T, MT>(ring, slab_off, aux, lane, acc); break;
+#define GQ_CONSUME(T) case T: ok = consume<T, MT>(ring, slab_off, aux, lane, acc, ar_prev); break;
         switch (type) {
             GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
             GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS) GQ_CONSUME(GQ_IQ3_XXS)
@@ -1195,7 +1224,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         if (ncols > 0) {
             if (((col0 | ncols | (int)p.n_total) & 1) && lane == 0) report_status(p.status, GQ_DEV_BAD_SHAPE);    // pairs of columns travel together
             else fused_allreduce_block(p, reinterpret_cast<const uint32_t *>(blk), (int)(blockIdx.x / (unsigned)p.split) * GQ_CONSUMER_WARPS + warp,
-                                       col0 + warp * 16, ncols, lane);
+                                       col0 + warp * 16, ncols, lane, ar_prev);
         }
         return;
     }
@@ -1229,7 +1258,7 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const float *__restri
 // C ABI
 // ---------------------------------------------------------------------------------------------------
 static int ensure_tables() {
-    // per-device one-time upload of the two format tables into constant memory
+    // per-device one-time upload of the format tables
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
@@ -1648,7 +1677,7 @@ extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K
 // rounding).  No loads from remote memory, no multicast.  Two slot sets alternate by call parity; the call
 // number lives in device memory (one counter per CTA) so a captured CUDA graph replays correctly.
 // The reference has no collective of its own on this path (docs/multi-gpu.md:8-13 leaves it to vLLM's NCCL).
-#define GQ_AR_CTAS 16
+#define GQ_AR_CTAS 32
 
 struct ArPeers {
     uint8_t *buf[GQ_AR_MAX_WORLD];      // data area of each rank's buffer: [2 sets][world][slot_bytes]
@@ -1697,11 +1726,18 @@ __global__ void __launch_bounds__(256) allreduce_push_kernel(const uint4 *__rest
     const uint8_t *base = peers.buf[rank] + (int64_t)set * world * slot_bytes;
     for (int64_t i = v0 + threadIdx.x; i < v1; i += 256) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < world; ++r) {
-            const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(base + (int64_t)r * slot_bytes) + i);
-            const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&v);
+        // all ranks' vectors are requested before any is added (one trip to the L2 instead of one per rank)
+        uint4 v[GQ_AR_MAX_WORLD];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        for (int r = 0; r < GQ_AR_MAX_WORLD; ++r)
+            if (r < world) v[r] = __ldcg(reinterpret_cast<const uint4 *>(base + (int64_t)r * slot_bytes) + i);
+#pragma unroll
+        for (int r = 0; r < GQ_AR_MAX_WORLD; ++r) {
+            if (r < world) {
+                const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&v[r]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(b[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+            }
         }
         uint4 o;
         __nv_bfloat162 *ob = reinterpret_cast<__nv_bfloat162 *>(&o);

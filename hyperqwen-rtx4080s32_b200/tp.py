@@ -94,7 +94,8 @@ class PushAllReduce:
         self._lib = L
 
     def status(self) -> int:
-        return int(self.buf[2 * 8 * 16 * 4 + 16 * 4:2 * 8 * 16 * 4 + 16 * 4 + 4].view(torch.int32).item())
+        off = 2 * 8 * 32 * 4 + 32 * 4      # behind the flags [2 sets][8 ranks][32 CTAs] and the 32 call counters (GQ_AR_CTAS in csrc/gq_b200.cu)
+        return int(self.buf[off:off + 4].view(torch.int32).item())
 
     def __call__(self, t: torch.Tensor) -> torch.Tensor:
         from ._lib import check
