@@ -706,15 +706,25 @@ struct Ring {
     const uint32_t *ar_counter;      // fused all-reduce: this warp's call counter (null: none), read early into ar_prev
 };
 
+// Fused all-reduce: lane 0 reads the warp's call counter as soon as the first stage is full — that stage holds
+// activations, so every launch in front of this one has finished and the counter is final — and the load's latency
+// passes during the multiplication instead of at the start of the exchange.  (The loop below waits on the same phase
+// again, which then returns at once.)
+__device__ __forceinline__ bool ring_read_counter(const Ring &r, int lane, uint32_t &ar_prev) {
+    if (!r.ar_counter) return true;
+    if (!mbar_wait(r.full, 0)) return false;
+    if (lane == 0) ar_prev = *reinterpret_cast<const volatile uint32_t *>(r.ar_counter);
+    return true;
+}
+
 // the consumer loop of one warp for a CTA whose shard is of TYPE: waits for each stage, processes its slab,
 // releases the stage.  Returns false if a bounded wait ran out.
 template <int TYPE, int MT>
 __device__ __forceinline__ bool consume(const Ring &r, int slab_off, const DecAux &aux, int lane, float (&acc)[MT][4], uint32_t &ar_prev) {
     float z[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!ring_read_counter(r, lane, ar_prev)) return false;
     for (int i = 0, s = 0, round = 0; i < r.nk; ++i) {
         if (!mbar_wait(r.full + s, round & 1)) return false;
-        // the first stage holds activations, so every launch in front of this one has finished and the counter is final
-        if (i == 0 && r.ar_counter && lane == 0) ar_prev = *reinterpret_cast<const volatile uint32_t *>(r.ar_counter);
         const uint8_t *st = r.smem + (size_t)s * r.stage_bytes;
         slab_kblock<TYPE, MT>(st + slab_off, st + r.wmax, aux, lane, acc, z);
         __syncwarp();
@@ -888,9 +898,9 @@ __device__ __forceinline__ void slab_kblock8(const uint8_t *slab, const uint8_t 
 
 template <int TYPE, int MT>
 __device__ __forceinline__ bool consume8(const Ring &r, int xs_off, int slab_off, const DecAux8 &aux, int lane, float (&acc)[MT][4], uint32_t &ar_prev) {
+    if (!ring_read_counter(r, lane, ar_prev)) return false;
     for (int i = 0, s = 0, round = 0; i < r.nk; ++i) {
         if (!mbar_wait(r.full + s, round & 1)) return false;
-        if (i == 0 && r.ar_counter && lane == 0) ar_prev = *reinterpret_cast<const volatile uint32_t *>(r.ar_counter);
         const uint8_t *st = r.smem + (size_t)s * r.stage_bytes;
         slab_kblock8<TYPE, MT>(st + slab_off, st + r.wmax, xs_off, aux, lane, acc);
         __syncwarp();
@@ -1036,30 +1046,32 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, GQ_CONSUMER_WARPS); }
         fence_barrier_init();
     }
-    // the codebook table of this CTA's type, at the start of the table region
-    if (p.cb_bytes) {
+    __syncthreads();
+    // the codebook table of this CTA's type, at the start of the table region: filled by the consumer warps while the
+    // producer's first copies are already on their way, closed by a barrier among the consumers only
+    if (p.cb_bytes && warp < GQ_CONSUMER_WARPS) {
         uint32_t *g32 = reinterpret_cast<uint32_t *>(grid_s);
         if ((ONLY == 0 || ONLY == GQ_IQ3_S) && type == GQ_IQ3_S) {
-            if constexpr (FORM) { for (int i = threadIdx.x; i < 512; i += blockDim.x) g32[i] = iq3s_grid_entry8(c_iq3s_grid[i]); }
-            else { for (int i = threadIdx.x; i < 512; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]); }
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 512; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq3s_grid[i]); }
+            else { for (int i = threadIdx.x; i < 512; i += 32 * GQ_CONSUMER_WARPS) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]); }
         }
         if ((ONLY == 0 || ONLY == GQ_IQ3_XXS) && type == GQ_IQ3_XXS) {
-            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += blockDim.x) { g32[i] = iq3s_grid_entry8(c_iq3xxs_grid[i]); g32[256 + i] = iq3xxs_sign_entry8((uint32_t)i); } }
-            else { for (int i = threadIdx.x; i < 256; i += blockDim.x) grid_s[i] = iq3s_grid_entry(c_iq3xxs_grid[i]); }
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) { g32[i] = iq3s_grid_entry8(c_iq3xxs_grid[i]); g32[256 + i] = iq3xxs_sign_entry8((uint32_t)i); } }
+            else { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) grid_s[i] = iq3s_grid_entry(c_iq3xxs_grid[i]); }
         }
         if ((ONLY == 0 || ONLY == GQ_IQ2_XXS) && type == GQ_IQ2_XXS) {
-            for (int i = threadIdx.x; i < 512; i += blockDim.x) g32[i] = iq3s_grid_entry8(c_iq2xxs_grid[i]);
-            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += blockDim.x) g32[512 + i] = iq3xxs_sign_entry8((uint32_t)i); }
+            for (int i = threadIdx.x; i < 512; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq2xxs_grid[i]);
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) g32[512 + i] = iq3xxs_sign_entry8((uint32_t)i); }
         }
         if ((ONLY == 0 || ONLY == GQ_IQ2_XS) && type == GQ_IQ2_XS) {
-            for (int i = threadIdx.x; i < 1024; i += blockDim.x) g32[i] = iq3s_grid_entry8(c_iq2xs_grid[i]);
-            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += blockDim.x) g32[1024 + i] = iq3xxs_sign_entry8((uint32_t)i); }
+            for (int i = threadIdx.x; i < 1024; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq2xs_grid[i]);
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) g32[1024 + i] = iq3xxs_sign_entry8((uint32_t)i); }
         }
         if ((ONLY == 0 || ONLY == GQ_IQ2_S) && type == GQ_IQ2_S) {
-            for (int i = threadIdx.x; i < 2048; i += blockDim.x) g32[i] = iq3s_grid_entry8(c_iq2s_grid[i]);
+            for (int i = threadIdx.x; i < 2048; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq2s_grid[i]);
         }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * GQ_CONSUMER_WARPS) : "memory");
     }
-    __syncthreads();
     // push-form split-K: a CTA may store into the split-0 CTA's shared memory only once that CTA is known to run;
     // every thread enters this rendezvous here and collects it just before its first remote store (or before the
     // closing barrier), long after everyone has arrived

@@ -418,8 +418,9 @@ def test_push_all_reduce_single_rank_degenerate(gq_lib):
         assert gq_lib.gq_allreduce_push(x.data_ptr(), y.data_ptr(), x.numel() * 2, 0, 1, ptrs, max_bytes, stream) == 0
         torch.cuda.synchronize()
         assert torch.equal(x, y)
-    counters = buf[1024:1024 + 64].view(torch.int32)
-    assert counters.tolist() == [3] * 16 and int(buf[1088:1092].view(torch.int32).item()) == 0
+    # header: flags [2 sets][8 ranks][32 CTAs] u32, then the 32 per-CTA call counters, then the status word
+    counters = buf[2048:2048 + 128].view(torch.int32)
+    assert counters.tolist() == [3] * 32 and int(buf[2176:2180].view(torch.int32).item()) == 0
     x = synth.activations(8, 5120, device=dev())
     g = torch.cuda.CUDAGraph()
     s = torch.cuda.Stream()
@@ -432,6 +433,6 @@ def test_push_all_reduce_single_rank_degenerate(gq_lib):
     for _ in range(3):
         g.replay()
     torch.cuda.synchronize()
-    assert torch.equal(x, before) and counters.tolist() == [6] * 16
+    assert torch.equal(x, before) and counters.tolist() == [6] * 32
     assert gq_lib.gq_allreduce_push(x.data_ptr(), x.data_ptr(), max_bytes + 16, 0, 1, ptrs, max_bytes, stream) == -2
     assert gq_lib.gq_allreduce_push(x.data_ptr(), x.data_ptr(), 32, 1, 1, ptrs, max_bytes, stream) == -3
