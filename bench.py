@@ -538,6 +538,7 @@ def run_ours(args):
 #   python bench.py --sweep decode --types Q4_K Q6_K --shapes gate kv --m 1 8 [--split 1 2] [--eager --iters 3]
 #   python bench.py --sweep prefill --types Q4_K --shapes gate_up down --m 512 2048 8192
 #   python bench.py --sweep neighbours --sweep-m 1 8      (silu_and_mul / add + RMSNorm folded into the layer behind them)
+#   python bench.py --sweep served --sweep-m 1 8          (the linear layers of the served checkpoint's own tensor list)
 # Decode: for each type x shape x batch the grouped kernel alone (activations prepared beforehand) and the whole call
 # (prepare + kernel + partial sum) as CUDA-graph replays over distinct weight copies totalling more than the L2, median of
 # 7 — the reference's timing method (gguf-plugin/test_gluon_kq_gpu.py:198-245) —, microseconds and GB/s of raw GGUF block
@@ -637,6 +638,58 @@ def sweep_neighbours(a, dev) -> None:
             _say(f"M={m:2} {name:32}: {1e3 * _graph_time(fn, layers):7.2f} us per layer", flush=True)
 
 
+def sweep_served(a, dev) -> None:
+    """The linear layers of the checkpoint the reference serves (names, shapes and GGML types from the tensor list
+    tests/golden/qwen35_tensor_names.json; values synthetic): every quantized 2-D weight of the 64 blocks through the
+    loader's name map — q / k / v and gate / up fused as vLLM fuses them — plus the LM head, one pass over all of them per
+    step as a CUDA graph; milliseconds and GB/s of raw GGUF block bytes.  The type mix is the file's own (IQ3_S, IQ4_XS,
+    IQ3_XXS, Q4_K, IQ2_S, ...), not the benchmark's eleven-type draw."""
+    import collections
+    import json
+
+    from hyperqwen_rtx4080s32_b200 import linear, loader
+
+    fx = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests", "golden", "qwen35_tensor_names.json")))
+    order = {"q": 0, "k": 1, "v": 2, 0: 0, 1: 1, None: 0}
+    layers, skipped, by_type, seed = [], [], collections.Counter(), 0
+    groups = [(f"blk.{b}.", t) for b, t in sorted(fx["blocks"].items(), key=lambda kv: int(kv[0]))] + [("", fx["top"])]
+    for prefix, tensors in groups:
+        pending = collections.OrderedDict()
+        for name, tname, shape in tensors:
+            mapped = loader.map_tensor_name(prefix + name)
+            if len(shape) != 2 or mapped is None or tname in ("F32", "F16", "BF16") or name == "token_embd.weight":
+                continue
+            if mapped.module is None and name != "output.weight":
+                continue
+            if tname not in F.TYPE_IDS:
+                skipped.append(f"{prefix}{name} ({tname})")
+                continue
+            k, n = shape
+            pending.setdefault(mapped.merged or mapped.module or "lm_head", []).append((order[mapped.shard_id], mapped.shard_id, F.TYPE_IDS[tname], n, k))
+        for key, shards in pending.items():
+            shards.sort(key=lambda sh: sh[0])
+            k = shards[0][4]
+            lin = linear.GGUFLinear(k, [sh[3] for sh in shards])
+            for _, sid, t, n, _ in shards:
+                seed += 1
+                lin.load_shard(synth.random_blocks(n, k, t, seed=seed, device=dev), t, sid if len(shards) > 1 else None)
+                by_type[F.TYPE_NAMES[t]] += F.raw_bytes(t, n, k)
+            layers.append((lin.finalize(), k))
+        torch.cuda.empty_cache()
+    total = sum(by_type.values())
+    _say(f"{len(layers)} linear layers, {total / 1e9:.2f} GB of raw blocks: " + ", ".join(f"{t} {100.0 * b / total:.1f} %" for t, b in by_type.most_common())
+         + (f"; not built: {', '.join(skipped)}" if skipped else ""))
+    for m in a.m:
+        xs = {k: synth.activations(m, k, device=dev) for k in {k for _, k in layers}}
+
+        def step():
+            for lin, k in layers:
+                lin(xs[k])
+
+        ms = _graph_time(step, 1)
+        _say(f"M={m:2}: {ms:7.3f} ms per pass over the {len(layers)} layers = {total / ms / 1e6:6.0f} GB/s ({total / ms / 1e6 / 6555.5:.2f} of the measured copy bandwidth)", flush=True)
+
+
 def run_sweep(a) -> None:
     import numpy as np  # noqa: F401
     import torch
@@ -653,6 +706,8 @@ def run_sweep(a) -> None:
         return sweep_prefill(a, dev)
     if a.sweep == "neighbours":
         return sweep_neighbours(a, dev)
+    if a.sweep == "served":
+        return sweep_served(a, dev)
     for tn in a.types:
         t = F.TYPE_IDS[tn]
         for sn in a.shapes:
@@ -721,7 +776,7 @@ def main():
     ap.add_argument("--no-m-sweep", action="store_true", help="skip the other batch sizes of the config (M = 1, 4, 64; tensor parallel: 1, 64, 4096)")
     ap.add_argument("--unfused-allreduce", action="store_true", help="tensor parallel: all-reduce with the library's separate push kernel instead of inside the grouped kernel")
     ap.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: use NCCL for the row-parallel all-reduce instead of the library's push kernel")
-    ap.add_argument("--sweep", choices=["decode", "prefill", "neighbours"], help="per-type sweep instead of the benchmark line (prints a table)")
+    ap.add_argument("--sweep", choices=["decode", "prefill", "neighbours", "served"], help="per-type sweep instead of the benchmark line (prints a table)")
     ap.add_argument("--types", nargs="*", default=[], help="--sweep: GGML type names (default all)")
     ap.add_argument("--shapes", nargs="*", default=[], help="--sweep: q kv o gate down (decode; or NxK), gate_up down q (prefill)")
     ap.add_argument("--sweep-m", nargs="*", type=int, default=[], help="--sweep: batch sizes")

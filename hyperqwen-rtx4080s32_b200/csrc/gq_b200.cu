@@ -1056,16 +1056,14 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             else { for (int i = threadIdx.x; i < 512; i += 32 * GQ_CONSUMER_WARPS) grid_s[i] = iq3s_grid_entry(c_iq3s_grid[i]); }
         }
         if ((ONLY == 0 || ONLY == GQ_IQ3_XXS) && type == GQ_IQ3_XXS) {
-            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) { g32[i] = iq3s_grid_entry8(c_iq3xxs_grid[i]); g32[256 + i] = iq3xxs_sign_entry8((uint32_t)i); } }
+            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq3xxs_grid[i]); }
             else { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) grid_s[i] = iq3s_grid_entry(c_iq3xxs_grid[i]); }
         }
         if ((ONLY == 0 || ONLY == GQ_IQ2_XXS) && type == GQ_IQ2_XXS) {
             for (int i = threadIdx.x; i < 512; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq2xxs_grid[i]);
-            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) g32[512 + i] = iq3xxs_sign_entry8((uint32_t)i); }
         }
         if ((ONLY == 0 || ONLY == GQ_IQ2_XS) && type == GQ_IQ2_XS) {
             for (int i = threadIdx.x; i < 1024; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq2xs_grid[i]);
-            if constexpr (FORM) { for (int i = threadIdx.x; i < 256; i += 32 * GQ_CONSUMER_WARPS) g32[1024 + i] = iq3xxs_sign_entry8((uint32_t)i); }
         }
         if ((ONLY == 0 || ONLY == GQ_IQ2_S) && type == GQ_IQ2_S) {
             for (int i = threadIdx.x; i < 2048; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq2s_grid[i]);

@@ -28,7 +28,7 @@ enum { GQ_S32 = 0, GQ_F32 = 1, GQ_S16 = 2, GQ_FOLD = 3 };
 
 struct DecAux8 {
     const uint32_t *grid;        // shared memory: the codebook of the CTA's type, four magnitude bytes per entry in quad byte order
-                                 // (IQ3_S 512 entries; IQ3_XXS 256 entries followed by the 128 x 2 sign words)
+                                 // (IQ3_S 512, IQ3_XXS 256 entries; IQ2_*: two words per entry)
     Iq4Table iq4;                // the IQ4 codebook as signed bytes
 };
 
@@ -523,12 +523,14 @@ struct Dec8<GQ_IQ3_S> {
 };
 
 // ---- IQ3_XXS ---------------------------------------------------------------------------------------
-// Shared memory: 256 grid words, then 128 x 2 sign words: entry 2 f + n = spread_sign of nibble n of the 8-bit mask of
-// sign index f (the index with its parity as bit 7).
-#define GQ_IQ3XXS8_SMEM_BYTES 2048
-GQ_HD inline uint32_t iq3xxs_sign_entry8(uint32_t i) {
-    const uint32_t f = i >> 1, mask = f | ((popc32(f) & 1u) << 7);
-    return spread_sign((mask >> (4 * (i & 1))) & 0xFu);
+// Shared memory: the 256 grid words.  The lane's four sign bits come from the stored 7-bit index by arithmetic (the index
+// with its parity as bit 7, then the lane's nibble): a 128-entry table of them in shared memory was measured 12-14 %
+// slower — with the grid lookups the type is bound by shared-memory gathers, not by the integer pipe.
+// `r`: the sign-and-scale word rotated so that the lane's index sits at bits 3..9; shn: 4 x (t & 1).
+GQ_HD inline uint32_t sign_index_quad(uint32_t r, int shn) {
+    const uint32_t f = (r >> 3) & 0x7Fu;
+    const uint32_t mask = f | (popc32(f) << 7);          // bits above 7 fall outside the nibble
+    return spread_sign((mask >> shn) & 0xFu);
 }
 
 template <>
@@ -540,12 +542,12 @@ struct Dec8<GQ_IQ3_XXS> {
     uint32_t sw[2][8];   // the sign-and-scale word of each sub-block
     uint32_t dd[2];
     int rot0, rot1;      // rotate counts that bring the lane's sign index of the first / second run of a sub-block to bits 3..9
+    int shn;             // 4 (t & 1): the lane's nibble of an 8-bit sign mask
     const uint32_t *grid;
-    const uint8_t *signs;   // the sign words, offset by the lane's nibble
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
         grid = aux.grid;
         const int t = lane & 3;
-        signs = reinterpret_cast<const uint8_t *>(aux.grid + 256) + 4 * (t & 1);
+        shn = 4 * (t & 1);
         rot0 = (7 * (t >> 1) - 3) & 31;
         rot1 = 7 * (2 + (t >> 1)) - 3;
 #pragma unroll
@@ -562,8 +564,7 @@ struct Dec8<GQ_IQ3_XXS> {
     GQ_HD uint32_t quad() const {
         const uint32_t e = grid[(uint32_t)ubyte<(R & 3)>(w4(q[H], R >> 2))];
         const uint32_t w = sw[H][R >> 1];
-        const uint32_t off = rotr32(w, (R & 1) ? rot1 : rot0) & 0x3F8u;      // 8 x sign index
-        const uint32_t one = *reinterpret_cast<const uint32_t *>(signs + off);
+        const uint32_t one = sign_index_quad(rotr32(w, (R & 1) ? rot1 : rot0), shn);
         return (e ^ (one * 0xFFu)) + one;       // negated bytes where the sign bit is set
     }
     template <int S>
@@ -580,9 +581,9 @@ struct Dec8<GQ_IQ3_XXS> {
 
 // ---- IQ2_XXS / IQ2_XS / IQ2_S --------------------------------------------------------------------------
 // A grid entry holds eight magnitudes; the lanes t = 0, 1 (2, 3) of a row share the entry of the first (second) eight
-// weights of a run and take its word t & 1.  Shared memory: the grid as two words per entry, each in quad byte order,
-// then (IQ2_XXS, IQ2_XS) the 128 x 2 sign words of IQ3_XXS.  weight = d (2 s + 1) / 8 x magnitude x sign
-// (gguf-plugin/gluon/iq2.py:6-23).
+// weights of a run and take its word t & 1.  Shared memory: the grid as two words per entry, each in quad byte order;
+// the 7-bit sign indices of IQ2_XXS and IQ2_XS are turned into masks by arithmetic as for IQ3_XXS.
+// weight = d (2 s + 1) / 8 x magnitude x sign (gguf-plugin/gluon/iq2.py:6-23).
 
 // bytes tp, 2 + tp of two words -> one word (runtime tp): the even or the odd bytes of eight
 GQ_HD inline uint32_t pick_alt_bytes(uint32_t a, uint32_t b, int tp) { return prmt(a, b, 0x6420u + 0x1111u * (uint32_t)tp); }
@@ -595,12 +596,12 @@ struct Dec8<GQ_IQ2_XXS> {
     uint32_t q[2][4];    // grid-index byte of run r in byte r & 3 of word r >> 2
     uint32_t sw[2][8];   // the sign-and-scale word of each sub-block
     uint32_t dd[2];
-    int rot0, rot1;
-    const uint8_t *grid, *signs;    // both offset by the lane's half of an entry
+    int rot0, rot1, shn;
+    const uint8_t *grid;            // offset by the lane's half of an entry
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
         const int t = lane & 3, tp = t >> 1;
         grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
-        signs = reinterpret_cast<const uint8_t *>(aux.grid + 512) + 4 * (t & 1);
+        shn = 4 * (t & 1);
         rot0 = (7 * tp - 3) & 31;
         rot1 = 7 * (2 + tp) - 3;
 #pragma unroll
@@ -620,7 +621,7 @@ struct Dec8<GQ_IQ2_XXS> {
     GQ_HD uint32_t quad() const {
         const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + 8 * (uint32_t)ubyte<(R & 3)>(q[H][R >> 2]));
         const uint32_t w = sw[H][R >> 1];
-        const uint32_t one = *reinterpret_cast<const uint32_t *>(signs + (rotr32(w, (R & 1) ? rot1 : rot0) & 0x3F8u));
+        const uint32_t one = sign_index_quad(rotr32(w, (R & 1) ? rot1 : rot0), shn);
         return (e ^ (one * 0xFFu)) + one;
     }
     template <int S>
@@ -648,11 +649,12 @@ struct Dec8<GQ_IQ2_XS> {
     static constexpr int NCORR = 0;
     uint32_t v[2][8];    // the halfword (9-bit grid index, 7-bit sign index) of run r in half r & 1 of word r >> 1
     uint32_t sce[2][2], sco[2][2], dd[2];
-    const uint8_t *grid, *signs;
+    int shn;
+    const uint8_t *grid;
     GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
         const int t = lane & 3, tp = t >> 1;
         grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
-        signs = reinterpret_cast<const uint8_t *>(aux.grid + 1024) + 4 * (t & 1);
+        shn = 4 * (t & 1);
         const uint32_t sel = 0x5410u + 0x2222u * (uint32_t)tp;     // halfword tp of each of two words
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -671,9 +673,8 @@ struct Dec8<GQ_IQ2_XS> {
     GQ_HD uint32_t quad() const {
         const uint32_t w = v[H][R >> 1];
         const uint32_t goff = (R & 1) ? (w >> 13) & 0xFF8u : (w << 3) & 0xFF8u;
-        const uint32_t soff = (R & 1) ? (w >> 22) & 0x3F8u : (w >> 6) & 0x3F8u;
         const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + goff);
-        const uint32_t one = *reinterpret_cast<const uint32_t *>(signs + soff);
+        const uint32_t one = sign_index_quad((R & 1) ? w >> 22 : w >> 6, shn);
         return (e ^ (one * 0xFFu)) + one;
     }
     template <int R>

@@ -68,8 +68,7 @@ GQ_HD inline int gq_type_chunks(int type) {
 }
 
 // Codebook types keep a table of grid entries in shared memory while a kernel decodes them.  Kind index of a type
-// (-1: not a codebook type), and the table's bytes in the integer form (form 1: magnitudes as bytes, plus 1 KB of sign
-// words for the types that store 7-bit sign indices) and in the fp16 form (form 0).
+// (-1: not a codebook type), and the table's bytes in the integer form (form 1: magnitudes as bytes) and in the fp16 form (form 0).
 GQ_HD inline int gq_cb_kind(int type) {
     switch (type) {
         case GQ_IQ3_S: return 0;
@@ -84,9 +83,9 @@ GQ_HD inline int gq_cb_kind(int type) {
 GQ_HD inline int gq_cb_bytes(int kind, int form) {
     switch (kind) {
         case 0: return form ? 2048 : 4096;     // IQ3_S: 512 entries of 4 bytes / of two fp16 pairs
-        case 1: return 2048;                   // IQ3_XXS: 256 entries of 4 bytes + sign words / of two fp16 pairs
-        case 2: return form ? 3072 : 2048;     // IQ2_XXS: 256 entries of 8 bytes (+ sign words)
-        case 3: return form ? 5120 : 4096;     // IQ2_XS: 512 entries of 8 bytes (+ sign words)
+        case 1: return form ? 1024 : 2048;     // IQ3_XXS: 256 entries of 4 bytes / of two fp16 pairs
+        case 2: return 2048;                   // IQ2_XXS: 256 entries of 8 bytes
+        case 3: return 4096;                   // IQ2_XS: 512 entries of 8 bytes
         case 4: return 8192;                   // IQ2_S: 1024 entries of 8 bytes
         default: return 0;
     }

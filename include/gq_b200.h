@@ -9,7 +9,7 @@
  *
  * Conventions
  *   - Every function returns an int status: 0 ok; < 0 the arguments were rejected on the host and
- *     nothing was launched (GQ_ERR_*); > 0 is only ever reported through gq_read_status (a kernel hit a
+ *     nothing was launched (GQ_ERR_*); > 0 is only ever reported through gq_read_status / gq_device_status (a kernel hit a
  *     bounded wait's limit).  Nothing aborts, traps or spins without a limit.
  *   - Pointers named *_dev are device pointers owned by the caller; `stream` is a cudaStream_t passed
  *     as void*.  No entry point allocates or frees device memory, or synchronises, except where stated.
@@ -228,7 +228,9 @@ int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const 
                     int64_t workspace_bytes, void *stream);
 
 /* Reads the device status word of the last call on this workspace (synchronises the stream): 0, or
- * a positive GQ_DEV_* code (1: a bounded wait ran out). */
+ * a positive GQ_DEV_* code (1: a bounded wait ran out; 2: a shape or a tile's type contradicts the call's arguments —
+ * an odd column count in the fused all-reduce, a tile that is not of the single type run_info names, a codebook type run_info
+ * does not announce; the CTA concerned computed nothing). */
 int gq_read_status(const void *workspace_dev, int64_t workspace_bytes, void *stream);
 
 /* The largest device status code any kernel of this library has reported on the current device since the word was
