@@ -67,8 +67,8 @@ def _write_gguf(path, tensors):
 def _tiny_model():
     k, inter = 512, 768
     spec = [("blk.3.attn_q.weight", 256, k, F.Q4_K), ("blk.3.attn_k.weight", 64, k, F.IQ3_S), ("blk.3.attn_v.weight", 64, k, F.Q6_K),
-            ("blk.3.attn_output.weight", k, 256, F.IQ4_XS), ("blk.3.ffn_gate.weight", inter, k, F.Q2_K), ("blk.3.ffn_up.weight", inter, k, F.Q2_K),
-            ("blk.3.ffn_down.weight", k, inter, F.Q5_K), ("output.weight", 1000, k, F.Q4_K), ("token_embd.weight", 1000, k, F.Q8_0)]
+            ("blk.3.attn_output.weight", k, 256, F.IQ4_XS), ("blk.3.ffn_gate.weight", inter, k, F.IQ3_XXS), ("blk.3.ffn_up.weight", inter, k, F.IQ2_XS),
+            ("blk.3.ffn_down.weight", k, inter, F.IQ2_S), ("output.weight", 1000, k, F.Q4_K), ("token_embd.weight", 1000, k, F.IQ2_S)]      # the served file's kinds of type
     tensors = [(n, synth.random_blocks(no, kk, t, seed=300 + i).numpy(), t) for i, (n, no, kk, t) in enumerate(spec)]
     tensors.append(("blk.3.attn_norm.weight", np.ones(k, dtype=np.float32), None))
     tensors.append(("v.blk.0.ln1.weight", np.ones(8, dtype=np.float32), None))
@@ -118,5 +118,5 @@ def test_layers_loaded_from_a_gguf_file_match_the_oracle(tmp_path):
     table = torch.from_numpy(np.array(emb.data, copy=True)).reshape(emb.shape[0], -1).to(dev)
     ids = torch.tensor([[0, 999, 17], [17, 5, 640]], device=dev)
     got = loader.embedding_lookup(table, emb.ggml_type, ids, dtype=torch.float32).cpu().numpy()
-    want = oracle.dequantize(raw["token_embd.weight"], F.Q8_0)[ids.cpu().numpy().reshape(-1)].reshape(2, 3, -1)
+    want = oracle.dequantize(raw["token_embd.weight"], F.IQ2_S)[ids.cpu().numpy().reshape(-1)].reshape(2, 3, -1)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
