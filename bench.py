@@ -586,7 +586,7 @@ def sweep_prefill(a, dev) -> None:
                 x = synth.activations(m, k, device=dev)
                 y = torch.empty((m, n_total), dtype=torch.bfloat16, device=dev)
                 for _ in range(2):
-                    ops.prefill_gemm(x, packed, d1, n_total, out=y)
+                    ops.prefill_gemm(x, packed, d1, n_total, out=y, wtypes=[t] * len(n_outs))
                 torch.cuda.synchronize()
                 if a.eager:
                     _say(f"{tn:7} {sn:8} M={m}: eager", flush=True)
@@ -595,7 +595,7 @@ def sweep_prefill(a, dev) -> None:
                 for _ in range(5):
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
-                    ops.prefill_gemm(x, packed, d1, n_total, out=y)
+                    ops.prefill_gemm(x, packed, d1, n_total, out=y, wtypes=[t] * len(n_outs))
                     e1.record()
                     torch.cuda.synchronize()
                     ts.append(e0.elapsed_time(e1))

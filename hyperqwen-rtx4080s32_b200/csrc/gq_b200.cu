@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(256) unrepack_kernel(int type, int B, const ui
 __device__ uint32_t c_iq3s_grid[512];
 __device__ uint32_t c_iq3xxs_grid[256];
 __device__ uint32_t c_iq2xxs_grid[512], c_iq2xs_grid[1024], c_iq2s_grid[2048];    // two words per entry
+__device__ uint32_t c_iq1_grid[4096];      // two words per entry, a byte is 8 g + 16
 __constant__ int8_t c_iq4_kvalues[16];
 
 // A bounded wait that runs out is reported twice: in the status word of the launch's workspace (gq_read_status) and in
@@ -206,6 +207,16 @@ __device__ float deq_one(int type, const uint8_t *b, int w) {
             const float db = __fmul_rn(__fmul_rn(h2f(b), 0.5f + (float)sc), 0.25f);
             const float mag = (float)((c_iq2s_grid[2 * idx + (j >> 2)] >> (8 * (j & 3))) & 0xFF);
             const float v = __fmul_rn(db, mag); return ((b[34 + g] >> j) & 1) ? -v : v; }
+        case GQ_IQ1_M: { const int g = w >> 3, j = w & 7;
+            const uint32_t s0 = b[48] | (b[49] << 8), s1 = b[50] | (b[51] << 8), s2 = b[52] | (b[53] << 8), s3 = b[54] | (b[55] << 8);
+            const uint32_t dv = (s0 >> 12) | ((s1 >> 8) & 0xF0u) | ((s2 >> 4) & 0xF00u) | (s3 & 0xF000u);
+            const float d = __half2float(__ushort_as_half((unsigned short)dv));
+            const uint32_t nib = (b[32 + (g >> 1)] >> (4 * (g & 1))) & 0xFu, idx = b[g] | ((nib & 7u) << 8);
+            const uint32_t sw = (g >> 3) == 0 ? s0 : (g >> 3) == 1 ? s1 : (g >> 3) == 2 ? s2 : s3;
+            const float dl = __fmul_rn(d, (float)(2 * ((sw >> (3 * ((g >> 1) & 3))) & 7u) + 1));
+            const int byte = (int)((c_iq1_grid[2 * idx + (j >> 2)] >> (8 * (j & 3))) & 0xFF);
+            const float gv = (float)(byte - 16) * 0.125f;
+            return __fmul_rn(dl, gv + ((nib & 8u) ? -0.125f : 0.125f)); }
         case GQ_IQ4_XS: { const int ib = w >> 5, j = w & 31; const uint32_t sh = b[2] | (b[3] << 8);
             const int ls = (int)(((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
             const float dl = __fmul_rn(h2f(b), (float)ls);
@@ -1068,6 +1079,9 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         if ((ONLY == 0 || ONLY == GQ_IQ2_S) && type == GQ_IQ2_S) {
             for (int i = threadIdx.x; i < 2048; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq2s_grid[i]);
         }
+        if ((ONLY == 0 || ONLY == GQ_IQ1_M) && type == GQ_IQ1_M) {
+            for (int i = threadIdx.x; i < 4096; i += 32 * GQ_CONSUMER_WARPS) g32[i] = iq3s_grid_entry8(c_iq1_grid[i]);
+        }
         asm volatile("bar.sync 1, %0;" ::"n"(32 * GQ_CONSUMER_WARPS) : "memory");
     }
     // push-form split-K: a CTA may store into the split-0 CTA's shared memory only once that CTA is known to run;
@@ -1152,7 +1166,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
             switch (type) {
                 GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
                 GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS) GQ_CONSUME(GQ_IQ3_XXS)
-                GQ_CONSUME(GQ_IQ2_XXS) GQ_CONSUME(GQ_IQ2_XS) GQ_CONSUME(GQ_IQ2_S)
+                GQ_CONSUME(GQ_IQ2_XXS) GQ_CONSUME(GQ_IQ2_XS) GQ_CONSUME(GQ_IQ2_S) GQ_CONSUME(GQ_IQ1_M)
             }
         }
 #undef GQ_CONSUME
@@ -1164,7 +1178,7 @@ __global__ void __launch_bounds__(32 * (GQ_CONSUMER_WARPS + 1), MINB) gemv_group
         switch (type) {
             GQ_CONSUME(GQ_Q4_0) GQ_CONSUME(GQ_Q5_0) GQ_CONSUME(GQ_Q8_0) GQ_CONSUME(GQ_Q2_K) GQ_CONSUME(GQ_Q3_K) GQ_CONSUME(GQ_Q4_K)
             GQ_CONSUME(GQ_Q5_K) GQ_CONSUME(GQ_Q6_K) GQ_CONSUME(GQ_IQ4_NL) GQ_CONSUME(GQ_IQ3_S) GQ_CONSUME(GQ_IQ4_XS) GQ_CONSUME(GQ_IQ3_XXS)
-                GQ_CONSUME(GQ_IQ2_XXS) GQ_CONSUME(GQ_IQ2_XS) GQ_CONSUME(GQ_IQ2_S)
+                GQ_CONSUME(GQ_IQ2_XXS) GQ_CONSUME(GQ_IQ2_XS) GQ_CONSUME(GQ_IQ2_S) GQ_CONSUME(GQ_IQ1_M)
         }
 #undef GQ_CONSUME
     }
@@ -1278,6 +1292,7 @@ static int ensure_tables() {
     GQ_CUDA(cudaMemcpyToSymbol(c_iq2xxs_grid, GQ_IQ2XXS_GRID, sizeof GQ_IQ2XXS_GRID));
     GQ_CUDA(cudaMemcpyToSymbol(c_iq2xs_grid, GQ_IQ2XS_GRID, sizeof GQ_IQ2XS_GRID));
     GQ_CUDA(cudaMemcpyToSymbol(c_iq2s_grid, GQ_IQ2S_GRID, sizeof GQ_IQ2S_GRID));
+    GQ_CUDA(cudaMemcpyToSymbol(c_iq1_grid, GQ_IQ1_GRID, sizeof GQ_IQ1_GRID));
     GQ_CUDA(cudaMemcpyToSymbol(c_iq4_kvalues, GQ_IQ4_KVALUES, sizeof GQ_IQ4_KVALUES));
     if (dev < 64) done_mask.fetch_or(1ull << dev);
     return GQ_OK;
@@ -1434,7 +1449,7 @@ static int launch_gemv8_m8(const GemvParams &p, int64_t n_desc, cudaStream_t st,
     switch (only) {
 #define GQ_ONE(T) case T: return launch_gemv<1, 4, 1, T>(p, n_desc, st);
         GQ_ONE(GQ_Q4_0) GQ_ONE(GQ_Q5_0) GQ_ONE(GQ_Q8_0) GQ_ONE(GQ_Q2_K) GQ_ONE(GQ_Q3_K) GQ_ONE(GQ_Q4_K)
-        GQ_ONE(GQ_Q5_K) GQ_ONE(GQ_Q6_K) GQ_ONE(GQ_IQ4_NL) GQ_ONE(GQ_IQ3_S) GQ_ONE(GQ_IQ4_XS) GQ_ONE(GQ_IQ3_XXS) GQ_ONE(GQ_IQ2_XXS) GQ_ONE(GQ_IQ2_XS) GQ_ONE(GQ_IQ2_S)
+        GQ_ONE(GQ_Q5_K) GQ_ONE(GQ_Q6_K) GQ_ONE(GQ_IQ4_NL) GQ_ONE(GQ_IQ3_S) GQ_ONE(GQ_IQ4_XS) GQ_ONE(GQ_IQ3_XXS) GQ_ONE(GQ_IQ2_XXS) GQ_ONE(GQ_IQ2_XS) GQ_ONE(GQ_IQ2_S) GQ_ONE(GQ_IQ1_M)
 #undef GQ_ONE
         default: return launch_gemv<1, 4, 1, 0>(p, n_desc, st);
     }
@@ -1499,9 +1514,9 @@ static int gemv_grouped_impl(const void *x_dev, int64_t M, int64_t K, int64_t ld
     p.y = (__nv_bfloat16 *)y_dev; p.partials = ws.partials; p.status = ws.status;
     p.M = (int)M; p.K = (int)K; p.nb = (int)(K / GQ_QK); p.split = split; p.ldy = ldy; p.n_total = n_total;
     const int maxb = run_info & 0xFFFF;
-    if (maxb < 66 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
+    if (maxb < 56 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
     p.wbytes_max = 64 * maxb;   // every stage can hold a tile of any shard of the run
-    p.cb_bytes = gq_cb_region_max((run_info >> 22) & 31, form);
+    p.cb_bytes = gq_cb_region_max((run_info >> 22) & 63, form);
     // split-K up to 8 reduces inside a thread-block cluster (portable cluster size); larger splits keep the fp32
     // partials and the separate sum
     p.cluster = (split > 1 && split <= 8 && n_desc % split == 0) ? 1 : 0;
@@ -1844,7 +1859,10 @@ template <int NB>
 static int launch_prefill(PrefillParams &p, const __nv_bfloat16 *x, int64_t ldx, float *ex, uint8_t *xp, cudaStream_t st) {
     const int mt = (p.M + NB - 1) / NB;
     const size_t smem_base = 1024 + (size_t)GQ_PF_STAGES * (GQ_PF_A_BYTES + NB * 128) + 128;
-    const size_t smem = smem_base + (size_t)gq_cb_region_sum(p.cb_mask), smem_max = smem_base + (size_t)gq_cb_region_sum(31);
+    // the tables of the run's codebook types sit side by side; the opt-in covers every combination that fits a CTA at all
+    const size_t smem = smem_base + (size_t)gq_cb_region_sum(p.cb_mask);
+    const size_t smem_all = smem_base + (size_t)gq_cb_region_sum(63), smem_max = smem_all < 232448 ? smem_all : 232448;
+    if (smem > smem_max) return GQ_ERR_LIMIT;
     static std::atomic<unsigned long long> done_mask{0};
     int dev = 0;
     GQ_CUDA(cudaGetDevice(&dev));
@@ -1876,7 +1894,7 @@ extern "C" int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t 
         return GQ_ERR_ARG;
     if (n_desc > 0x7ffffffe || M > (int64_t)65535 * 64) return GQ_ERR_LIMIT;
     const int maxb = run_info & 0xFFFF;
-    if (maxb < 66 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
+    if (maxb < 56 || maxb > 272 || (maxb & 1)) return GQ_ERR_ARG;
     const int nbt = prefill_nb(M);
     const int split = prefill_split(n_desc, M, K / GQ_QK, nbt, device_sms());
     int *status; float *ex; uint8_t *xp; float *partials;
@@ -1886,7 +1904,7 @@ extern "C" int gq_gemm_prefill(const void *x_dev, int64_t M, int64_t K, int64_t 
     PrefillParams p;
     p.packed = (const uint8_t *)packed_dev; p.desc = desc_dev; p.n_desc = (int)n_desc; p.xp = xp; p.ex = ex;
     p.y = (__nv_bfloat16 *)y_dev; p.ldy = ldy; p.M = (int)M; p.K = (int)K; p.nb = (int)(K / GQ_QK); p.status = status;
-    p.split = split; p.partials = partials; p.n_total = n_total; p.cb_mask = (run_info >> 22) & 31;
+    p.split = split; p.partials = partials; p.n_total = n_total; p.cb_mask = (run_info >> 22) & 63;
     cudaStream_t st = (cudaStream_t)stream;
     switch (nbt) {
         case 64: return launch_prefill<64>(p, (const __nv_bfloat16 *)x_dev, ldx, ex, xp, st);

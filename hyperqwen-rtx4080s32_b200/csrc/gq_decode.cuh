@@ -925,6 +925,61 @@ struct Dec<GQ_IQ2_S> {
     template <int R> static constexpr float offs() { return 0.0f; }
 };
 
+// ---- IQ1_M (see gq_decode8.cuh for the format): the shared-memory grid holds 8 g + 16 per weight as bytes; the bytes become
+// fp16 through the 1024 + byte pattern and the subtraction takes 1024 + 16 -+ 1 off, leaving 8 g +- 1 exactly ----
+template <>
+struct Dec<GQ_IQ1_M> {
+    static constexpr int GROUP = 16;
+    static constexpr int NCORR = 0;
+    uint32_t q[2][4], qn[2][4];
+    uint2 sc[2];
+    uint32_t dd[2];
+    const uint8_t *grid;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux &aux) {
+        const int t = lane & 3, tp = t >> 1;
+        grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            const uint4 ia = ld16(slab + 32 * row), ib = ld16(slab + 32 * row + 16);
+            q[h][0] = pick_alt_bytes16(ia.x, ia.y, tp); q[h][1] = pick_alt_bytes16(ia.z, ia.w, tp);
+            q[h][2] = pick_alt_bytes16(ib.x, ib.y, tp); q[h][3] = pick_alt_bytes16(ib.z, ib.w, tp);
+            const uint4 hq = ld16(slab + 512 + 16 * row);
+            qn[h][0] = (hq.x >> (4 * tp)) & 0x0f0f0f0fu; qn[h][1] = (hq.y >> (4 * tp)) & 0x0f0f0f0fu;
+            qn[h][2] = (hq.z >> (4 * tp)) & 0x0f0f0f0fu; qn[h][3] = (hq.w >> (4 * tp)) & 0x0f0f0f0fu;
+            const uint2 w = ld8(slab + 768 + 8 * row);
+            sc[h] = w;
+            dd[h] = ((w.x >> 12) & 0xFu) | ((w.x >> 24) & 0xF0u) | ((w.y >> 4) & 0xF00u) | ((w.y >> 16) & 0xF000u);
+        }
+    }
+    template <int R>
+    GQ_HD void run(int h, uint32_t &a01, uint32_t &a23) const {
+        const uint32_t idxb = (q[h][R >> 2] >> (8 * (R & 3))) & 0xFFu;
+        const uint32_t nb = (qn[h][R >> 2] >> (8 * (R & 3))) & 0xFu;
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + 8 * (idxb | ((nb & 7u) << 8)));
+        const uint32_t c = h2k(1039) + (nb >> 3) * 0x00020002u;          // fp16 1039 (delta > 0: field - 15) or 1041 (field - 17)
+        a01 = hsub2(prmt(e, GQ_MAGICB, 0x5250u), c);
+        a23 = hsub2(prmt(e, GQ_MAGICB, 0x5351u), c);
+    }
+    template <int P>
+    GQ_HD void pair(uint32_t (&a)[2][4]) const {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            run<2 * P>(h, a[0][h], a[0][2 + h]);
+            run<2 * P + 1>(h, a[1][h], a[1][2 + h]);
+        }
+    }
+    template <int G>
+    GQ_HD void scale(float &s0, float &s1) const {
+        constexpr int hw = G >> 2, sh = 16 * (hw & 1) + 3 * (G & 3);
+        s0 = odd_scale_f32((((hw < 2) ? sc[0].x : sc[0].y) >> sh) & 7u);
+        s1 = odd_scale_f32((((hw < 2) ? sc[1].x : sc[1].y) >> sh) & 7u);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
+    static constexpr bool HAS_MIN = false;
+    template <int R> static constexpr float offs() { return 0.0f; }
+};
+
 // one entry of the IQ3_S / IQ3_XXS shared-memory grid: the four magnitude bytes of a grid word as two fp16 pairs
 GQ_HD inline uint2 iq3s_grid_entry(uint32_t w) {
     uint2 e;

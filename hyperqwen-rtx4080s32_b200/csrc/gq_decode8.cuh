@@ -738,4 +738,70 @@ struct Dec8<GQ_IQ2_S> {
     GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
 };
 
+// ---- IQ1_M: weight = d (2 s + 1) (g + delta), g in {-1, 0, 1} from a 2048-entry grid of eight, delta = +-1/8 per group of
+// eight, a 3-bit scale per 16 weights, the fp16 d spread over the top nibbles of the four scale halfwords (gguf-py
+// IQ1_M.dequantize_blocks; the reference has no kernel of its own for this type).  In eighths the weight is 8 g +- 1; the
+// grid in shared memory holds 8 g + 16 (bytes 8, 16, 24), so that adding +-1 to all four bytes of a word at once never
+// carries, and the constant 16 leaves through the correction MMA (run scales against the run sums). ----
+template <>
+struct Dec8<GQ_IQ1_M> {
+    static constexpr int SCHEME = GQ_S16;
+    static constexpr bool A_SIGNED = false;
+    static constexpr int NCORR = 1;
+    uint32_t q[2][4];    // low grid-index byte of run r in byte r & 3 of word r >> 2
+    uint32_t qn[2][4];   // the run's qh nibble, same place: bits 0..2 the index bits 8..10, bit 3 the sign of delta
+    uint2 sc[2];         // the four scale halfwords of a row
+    uint32_t dd[2];
+    int t;
+    const uint8_t *grid;
+    GQ_HD void load(const uint8_t *slab, int lane, const DecAux8 &aux) {
+        t = lane & 3;
+        const int tp = t >> 1;
+        grid = reinterpret_cast<const uint8_t *>(aux.grid) + 4 * (t & 1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = (lane >> 2) + 8 * h;
+            const uint4 ia = ld16(slab + 32 * row), ib = ld16(slab + 32 * row + 16);
+            q[h][0] = pick_alt_bytes(ia.x, ia.y, tp); q[h][1] = pick_alt_bytes(ia.z, ia.w, tp);
+            q[h][2] = pick_alt_bytes(ib.x, ib.y, tp); q[h][3] = pick_alt_bytes(ib.z, ib.w, tp);
+            const uint4 hq = ld16(slab + 512 + 16 * row);          // byte r: the nibbles of groups 2 r (low) and 2 r + 1
+            qn[h][0] = (hq.x >> (4 * tp)) & 0x0f0f0f0fu; qn[h][1] = (hq.y >> (4 * tp)) & 0x0f0f0f0fu;
+            qn[h][2] = (hq.z >> (4 * tp)) & 0x0f0f0f0fu; qn[h][3] = (hq.w >> (4 * tp)) & 0x0f0f0f0fu;
+            const uint2 w = ld8(slab + 768 + 8 * row);
+            sc[h] = w;
+            dd[h] = ((w.x >> 12) & 0xFu) | ((w.x >> 24) & 0xF0u) | ((w.y >> 4) & 0xF00u) | ((w.y >> 16) & 0xF000u);
+        }
+    }
+    template <int R, int H>
+    GQ_HD uint32_t quad() const {
+        const uint32_t idxb = (uint32_t)ubyte<(R & 3)>(q[H][R >> 2]);
+        const uint32_t nb = (uint32_t)ubyte<(R & 3)>(qn[H][R >> 2]);
+        const uint32_t idx = or_and(idxb, nb << 8, 0x700u);
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(grid + 8 * idx);
+        return e + 0x01010101u - (nb >> 3) * 0x02020202u;
+    }
+    template <int R>
+    GQ_HD void step16(uint32_t (&a)[2]) const { a[0] = quad<R, 0>(); a[1] = quad<R, 1>(); }
+    template <int R>
+    GQ_HD void iscale16(int &s0, int &s1) const {
+        constexpr int hw = R >> 2, sh = 16 * (hw & 1) + 3 * (R & 3);
+        s0 = (int)(2u * ((((hw < 2) ? sc[0].x : sc[0].y) >> sh) & 7u) + 1u);
+        s1 = (int)(2u * ((((hw < 2) ? sc[1].x : sc[1].y) >> sh) & 7u) + 1u);
+    }
+    GQ_HD void kscale(float &d0, float &d1) const { d0 = 0.125f * f16bits(dd[0]); d1 = 0.125f * f16bits(dd[1]); }
+    // weight x 8 = field - 16: A'' = 2 s + 1 of runs 4t..4t+3 (the scale halfword t), factor 16 d / 8
+    GQ_HD void corr(uint32_t (&a)[4], float (&f)[2]) const {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t w = (t & 2) ? sc[h].y : sc[h].x;
+            const uint32_t hw = (t & 1) ? w >> 16 : w;
+            const uint32_t b = (2u * (hw & 7u) + 1u) | ((2u * ((hw >> 3) & 7u) + 1u) << 8) | ((2u * ((hw >> 6) & 7u) + 1u) << 16) |
+                               ((2u * ((hw >> 9) & 7u) + 1u) << 24);
+            a[h] = hsub2(bytes_h2(b, 0x5150u), h2k(1024));
+            a[2 + h] = hsub2(bytes_h2(b, 0x5352u), h2k(1024));
+            f[h] = 2.0f * f16bits(dd[h]);
+        }
+    }
+};
+
 }  // namespace gq

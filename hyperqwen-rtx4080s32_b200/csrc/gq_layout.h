@@ -22,7 +22,8 @@
 
 enum GqType {
     GQ_Q4_0 = 2, GQ_Q5_0 = 6, GQ_Q8_0 = 8, GQ_Q2_K = 10, GQ_Q3_K = 11, GQ_Q4_K = 12, GQ_Q5_K = 13,
-    GQ_Q6_K = 14, GQ_IQ2_XXS = 16, GQ_IQ2_XS = 17, GQ_IQ3_XXS = 18, GQ_IQ4_NL = 20, GQ_IQ3_S = 21, GQ_IQ2_S = 22, GQ_IQ4_XS = 23
+    GQ_Q6_K = 14, GQ_IQ2_XXS = 16, GQ_IQ2_XS = 17, GQ_IQ3_XXS = 18, GQ_IQ4_NL = 20, GQ_IQ3_S = 21, GQ_IQ2_S = 22, GQ_IQ4_XS = 23,
+    GQ_IQ1_M = 29
 };
 
 #ifdef __CUDACC__
@@ -49,6 +50,7 @@ GQ_HD inline int gq_type_bytes(int type) {
         case GQ_IQ2_XXS: return 66;
         case GQ_IQ2_XS: return 74;
         case GQ_IQ2_S: return 82;
+        case GQ_IQ1_M: return 56;
         default: return 0;
     }
 }
@@ -76,10 +78,11 @@ GQ_HD inline int gq_cb_kind(int type) {
         case GQ_IQ2_XXS: return 2;
         case GQ_IQ2_XS: return 3;
         case GQ_IQ2_S: return 4;
+        case GQ_IQ1_M: return 5;
         default: return -1;
     }
 }
-#define GQ_CB_KINDS 5
+#define GQ_CB_KINDS 6
 GQ_HD inline int gq_cb_bytes(int kind, int form) {
     switch (kind) {
         case 0: return form ? 2048 : 4096;     // IQ3_S: 512 entries of 4 bytes / of two fp16 pairs
@@ -87,6 +90,7 @@ GQ_HD inline int gq_cb_bytes(int kind, int form) {
         case 2: return 2048;                   // IQ2_XXS: 256 entries of 8 bytes
         case 3: return 4096;                   // IQ2_XS: 512 entries of 8 bytes
         case 4: return 8192;                   // IQ2_S: 1024 entries of 8 bytes
+        case 5: return 16384;                  // IQ1_M: 2048 entries of 8 bytes
         default: return 0;
     }
 }
@@ -201,6 +205,12 @@ GQ_HD inline int gq_slab_src(int type, int p, int *row, int *byte) {
             if (q < 128) { *row = q >> 3; *byte = 66 + (q & 7); return 0; }
             q -= 128;
             *row = q >> 1; *byte = q & 1; return 0;
+        case GQ_IQ1_M:                             // per row the 32 low index bytes, then per row qh[16], then per row the four scale halfwords
+            if (q < 512) { *row = q >> 5; *byte = q & 31; return 0; }
+            q -= 512;
+            if (q < 256) { *row = q >> 4; *byte = 32 + (q & 15); return 0; }
+            q -= 256;
+            *row = q >> 3; *byte = 48 + (q & 7); return 0;
         case GQ_IQ2_S:                             // per row 32 index bytes, then per row 32 sign bytes, qh[8], scales[8], d
             if (q < 1024) { *row = (q >> 5) & 15; *byte = 2 + 32 * (q >> 9) + (q & 31); return 0; }
             q -= 1024;

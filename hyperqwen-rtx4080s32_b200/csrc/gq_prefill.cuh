@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
             case GQ_IQ2_XXS: for (int i = threadIdx.x; i < 512; i += blockDim.x) t32[i] = prmt(c_iq2xxs_grid[i], 0u, 0x3120u); break;
             case GQ_IQ2_XS: for (int i = threadIdx.x; i < 1024; i += blockDim.x) t32[i] = prmt(c_iq2xs_grid[i], 0u, 0x3120u); break;
             case GQ_IQ2_S: for (int i = threadIdx.x; i < 2048; i += blockDim.x) t32[i] = prmt(c_iq2s_grid[i], 0u, 0x3120u); break;
+            case GQ_IQ1_M: for (int i = threadIdx.x; i < 4096; i += blockDim.x) t32[i] = prmt(c_iq1_grid[i], 0u, 0x3120u); break;
         }
     }
     if (!has1) {
@@ -272,7 +273,7 @@ __global__ void __launch_bounds__(GQ_PF_THREADS, NB <= 64 ? 2 : 1) gemm_prefill_
             switch (dd[1]) {
                 GQ_PF(GQ_Q4_0) GQ_PF(GQ_Q5_0) GQ_PF(GQ_Q8_0) GQ_PF(GQ_Q2_K) GQ_PF(GQ_Q3_K) GQ_PF(GQ_Q4_K)
                 GQ_PF(GQ_Q5_K) GQ_PF(GQ_Q6_K) GQ_PF(GQ_IQ4_NL) GQ_PF(GQ_IQ3_S) GQ_PF(GQ_IQ4_XS) GQ_PF(GQ_IQ3_XXS)
-                GQ_PF(GQ_IQ2_XXS) GQ_PF(GQ_IQ2_XS) GQ_PF(GQ_IQ2_S)
+                GQ_PF(GQ_IQ2_XXS) GQ_PF(GQ_IQ2_XS) GQ_PF(GQ_IQ2_S) GQ_PF(GQ_IQ1_M)
             }
 #undef GQ_PF
         }

@@ -1,7 +1,8 @@
 """The GGML block types of the quantized-linear path: ids, sizes, names.
 
 The eleven types the benchmark's stack mixes (NORTH_STAR_TYPES) and the four codebook types the served checkpoint
-also holds (IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S: gguf-plugin/gluon/iq3xxs.py:1-20, gguf-plugin/gluon/iq2.py:1-39).
+also holds (IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S: gguf-plugin/gluon/iq3xxs.py:1-20, gguf-plugin/gluon/iq2.py:1-39; and IQ1_M,
+which the reference leaves to the plugin's row path).
 Block sizes agree with gguf.constants.GGML_QUANT_SIZES and with the constants the reference keeps
 (gguf-plugin/gluon/tiles.py:24-36, gguf-plugin/gluon/kq_tiles.py:22, gguf-plugin/gluon/q2k.py:34).
 Every type is handled in segments of 256 weights (one "k-block"): a K-quant superblock, or eight
@@ -16,11 +17,11 @@ SLAB_ROWS = 16    # output rows per lane-ordered slab inside a tile
 Q4_0, Q5_0, Q8_0 = 2, 6, 8
 Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 10, 11, 12, 13, 14
 IQ4_NL, IQ3_S, IQ4_XS = 20, 21, 23
-IQ2_XXS, IQ2_XS, IQ3_XXS, IQ2_S = 16, 17, 18, 22
+IQ2_XXS, IQ2_XS, IQ3_XXS, IQ2_S, IQ1_M = 16, 17, 18, 22, 29
 
 TYPE_NAMES = {Q4_0: "Q4_0", Q5_0: "Q5_0", Q8_0: "Q8_0", Q2_K: "Q2_K", Q3_K: "Q3_K", Q4_K: "Q4_K", Q5_K: "Q5_K",
               Q6_K: "Q6_K", IQ4_NL: "IQ4_NL", IQ3_S: "IQ3_S", IQ4_XS: "IQ4_XS", IQ3_XXS: "IQ3_XXS", IQ2_XXS: "IQ2_XXS",
-              IQ2_XS: "IQ2_XS", IQ2_S: "IQ2_S"}
+              IQ2_XS: "IQ2_XS", IQ2_S: "IQ2_S", IQ1_M: "IQ1_M"}
 TYPE_IDS = {v: k for k, v in TYPE_NAMES.items()}
 SUPPORTED_TYPES = frozenset(TYPE_NAMES)
 NORTH_STAR_TYPES = frozenset({Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ3_S, IQ4_XS})
@@ -28,7 +29,7 @@ NORTH_STAR_TYPES = frozenset({Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ
 # (weights per GGML block, bytes per GGML block)
 GGML_BLOCK = {Q4_0: (32, 18), Q5_0: (32, 22), Q8_0: (32, 34), IQ4_NL: (32, 18),
               Q2_K: (256, 84), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210),
-              IQ3_S: (256, 110), IQ4_XS: (256, 136), IQ3_XXS: (256, 98), IQ2_XXS: (256, 66), IQ2_XS: (256, 74), IQ2_S: (256, 82)}
+              IQ3_S: (256, 110), IQ4_XS: (256, 136), IQ3_XXS: (256, 98), IQ2_XXS: (256, 66), IQ2_XS: (256, 74), IQ2_S: (256, 82), IQ1_M: (256, 56)}
 # bytes of one row's 256-weight segment
 BYTES_PER_256 = {t: (QK // w) * b for t, (w, b) in GGML_BLOCK.items()}
 # types whose value has a per-group minimum term (w = d*sc*q - dmin*m)

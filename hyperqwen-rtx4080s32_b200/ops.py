@@ -309,10 +309,10 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
     return out
 
 
-def prefill_gemm(x: torch.Tensor, packed: torch.Tensor, desc1: torch.Tensor, n_total: int, out: torch.Tensor | None = None,
-                 wtypes: Sequence[int] | None = None) -> torch.Tensor:
+def prefill_gemm(x: torch.Tensor, packed: torch.Tensor, desc1: torch.Tensor, n_total: int, out: torch.Tensor | None = None, *,
+                 wtypes: Sequence[int]) -> torch.Tensor:
     """The large-batch path (tcgen05 dequant-GEMM): x bf16 [M, K] -> out bf16 [M, n_total]; desc1 is the run's
-    split-1 descriptor table; wtypes the run's GGML types (they size the shared-memory tables; every type assumed if absent)."""
+    split-1 descriptor table; wtypes the run's GGML types (they size the shared-memory tables)."""
     _need_cuda(x, "x")
     if x.dtype != torch.bfloat16 or x.dim() != 2:
         raise GqError(f"x must be bf16 [M, K], got {x.dtype} {tuple(x.shape)}")
@@ -330,7 +330,7 @@ def prefill_gemm(x: torch.Tensor, packed: torch.Tensor, desc1: torch.Tensor, n_t
         ws_bytes = check(L.gq_prefill_workspace_bytes(m, k, n_total, int(desc1.shape[0])), "gq_prefill_workspace_bytes")
     ws = torch.empty(ws_bytes + 1024, dtype=torch.uint8, device=x.device)
     base = (ws.data_ptr() + 1023) // 1024 * 1024
-    info = run_info(wtypes) if wtypes else 272 | (1 << 16) | (31 << 22)      # unknown types: the largest tile, every codebook table
+    info = run_info(wtypes)
     with torch.cuda.device(x.device):
         check(L.gq_gemm_prefill(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc1.data_ptr(), int(desc1.shape[0]), info, out.data_ptr(),
                                 out.stride(0), n_total, base, ws_bytes, _stream_ptr(x)), "gq_gemm_prefill")

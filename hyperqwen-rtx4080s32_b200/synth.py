@@ -21,7 +21,7 @@ from . import formats as F
 # byte offsets of the fp16 d (and dmin) fields inside one GGML block
 _D_OFF = {F.Q4_0: (0,), F.Q5_0: (0,), F.Q8_0: (0,), F.IQ4_NL: (0,), F.Q2_K: (80, 82), F.Q3_K: (108,),
           F.Q4_K: (0, 2), F.Q5_K: (0, 2), F.Q6_K: (208,), F.IQ3_S: (0,), F.IQ4_XS: (0,),
-          F.IQ3_XXS: (0,), F.IQ2_XXS: (0,), F.IQ2_XS: (0,), F.IQ2_S: (0,)}
+          F.IQ3_XXS: (0,), F.IQ2_XXS: (0,), F.IQ2_XS: (0,), F.IQ2_S: (0,), F.IQ1_M: ()}
 
 
 def random_blocks(n_out: int, k: int, wtype: int, seed: int, device="cpu", d_exp: int = -6) -> torch.Tensor:
@@ -36,6 +36,13 @@ def random_blocks(n_out: int, k: int, wtype: int, seed: int, device="cpu", d_exp
         u = torch.rand((n_out, nblk), device=device, generator=g) * 0.75 + 0.25
         val = (u * (2.0 ** d_exp if i == 0 else 2.0 ** (d_exp - 2))).to(torch.float16)
         raw[:, :, off:off + 2] = val.view(torch.uint8).reshape(n_out, nblk, 2)
+    if wtype == F.IQ1_M:
+        # the fp16 d of IQ1_M lives in the top nibbles of the four scale halfwords (bytes 49, 51, 53, 55)
+        u = torch.rand((n_out, nblk), device=device, generator=g) * 0.75 + 0.25
+        bits = (u * 2.0 ** d_exp).to(torch.float16).view(torch.int16).to(torch.int32) & 0xFFFF
+        for i in range(4):
+            hi = raw[:, :, 49 + 2 * i].to(torch.int32)
+            raw[:, :, 49 + 2 * i] = ((hi & 0x0F) | (((bits >> (4 * i)) & 0xF) << 4)).to(torch.uint8)
     return raw.reshape(n_out, nblk * bpb)
 
 
@@ -316,6 +323,35 @@ def _enc_iq2(w, wtype):
     return np.concatenate([dbytes.reshape(n, 2), qs], axis=1)
 
 
+def _enc_iq1_m(w):
+    """qs[32] | qh[16] | scales[8]: weight = d (2 s + 1) (g + delta), g in {-1, 0, 1}^8 from a 2048-entry grid, delta = +-1/8
+    per group of eight, a 3-bit scale per 16 weights, the fp16 d spread over the top nibbles of the scale halfwords."""
+    from gguf.quants import IQ1_M
+
+    IQ1_M.init_grid()
+    grid = IQ1_M.grid.reshape(2048, 8).astype(np.float32)
+    n = w.shape[0]
+    wb = w.reshape(n, 16, 16)
+    step_t = np.abs(wb).max(-1) / 1.125
+    d, dbytes = _f16(step_t.max(-1, keepdims=True) / 15.0)
+    s = np.clip(np.rint((_safe_div(step_t, d) - 1.0) / 2.0), 0, 7).astype(np.uint32)
+    step = np.broadcast_to((d * (2 * s.astype(np.float32) + 1))[..., None], wb.shape)
+    v = _safe_div(wb, step).reshape(n * 32, 8)
+    ip, im = _nearest_grid(v - 0.125, grid), _nearest_grid(v + 0.125, grid)
+    ep, em = ((grid[ip] + 0.125 - v) ** 2).sum(-1), ((grid[im] - 0.125 - v) ** 2).sum(-1)
+    neg = em < ep
+    idx = np.where(neg, im, ip).astype(np.uint32).reshape(n, 32)
+    nib = ((idx >> 8) & 7) | (neg.reshape(n, 32).astype(np.uint32) << 3)
+    qh = (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)
+    dbits = dbytes.reshape(n, 2).astype(np.uint32)
+    dv = dbits[:, 0] | (dbits[:, 1] << 8)
+    s4 = s.reshape(n, 4, 4)
+    sc = (s4[..., 0] | (s4[..., 1] << 3) | (s4[..., 2] << 6) | (s4[..., 3] << 9)).astype(np.uint32)
+    for i in range(4):
+        sc[:, i] |= ((dv >> (4 * i)) & 0xF) << 12
+    return np.concatenate([(idx & 0xFF).astype(np.uint8), qh, sc.astype("<u2").view(np.uint8).reshape(n, 8)], axis=1)
+
+
 def _enc_gguf(wtype):
     def enc(w):
         from gguf.constants import GGMLQuantizationType
@@ -327,7 +363,7 @@ def _enc_gguf(wtype):
 
 _ENCODERS = {F.Q4_K: _enc_q4_k, F.Q5_K: _enc_q5_k, F.Q2_K: _enc_q2_k, F.Q3_K: _enc_q3_k, F.Q6_K: _enc_q6_k,
              F.IQ4_NL: _enc_iq4_nl, F.IQ4_XS: _enc_iq4_xs, F.IQ3_S: _enc_iq3_s, F.IQ3_XXS: _enc_iq3_xxs,
-             F.IQ2_XXS: lambda w: _enc_iq2(w, F.IQ2_XXS), F.IQ2_XS: lambda w: _enc_iq2(w, F.IQ2_XS), F.IQ2_S: lambda w: _enc_iq2(w, F.IQ2_S),
+             F.IQ2_XXS: lambda w: _enc_iq2(w, F.IQ2_XXS), F.IQ2_XS: lambda w: _enc_iq2(w, F.IQ2_XS), F.IQ2_S: lambda w: _enc_iq2(w, F.IQ2_S), F.IQ1_M: _enc_iq1_m,
              F.Q8_0: _enc_gguf(F.Q8_0), F.Q4_0: _enc_gguf(F.Q4_0), F.Q5_0: _enc_gguf(F.Q5_0)}
 
 

@@ -14,7 +14,7 @@
  *   - Pointers named *_dev are device pointers owned by the caller; `stream` is a cudaStream_t passed
  *     as void*.  No entry point allocates or frees device memory, or synchronises, except where stated.
  *   - GGML type ids: Q4_0 2, Q5_0 6, Q8_0 8, Q2_K 10, Q3_K 11, Q4_K 12, Q5_K 13, Q6_K 14, IQ2_XXS 16, IQ2_XS 17,
- *     IQ3_XXS 18, IQ4_NL 20, IQ3_S 21, IQ2_S 22, IQ4_XS 23.  K must be a multiple of 256.
+ *     IQ3_XXS 18, IQ4_NL 20, IQ3_S 21, IQ2_S 22, IQ4_XS 23, IQ1_M 29.  K must be a multiple of 256.
  *   - Thread safety: re-entrant; one call at a time per workspace buffer.
  */
 #ifndef GQ_B200_H
@@ -87,9 +87,9 @@ int gq_split_for(int64_t n_tiles, int64_t nb, int64_t M, int avg_bytes_per_256, 
 
 /* Facts of a run the launchers size shared memory and pick a kernel by, packed in one int:
  *   bits 0..15   the largest bytes_per_256 of the run's types (a stage of the weight ring holds a tile of any shard)
- *   bit 16       the run holds a codebook type (IQ3_S, IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S)
+ *   bit 16       the run holds a codebook type (IQ3_S, IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S, IQ1_M)
  *   bits 17..21  the GGML type id when every shard has the same type (the per-type kernel serves it), else 0
- *   bits 22..26  which codebook types: IQ3_S, IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S in this order (their grid tables are
+ *   bits 22..27  which codebook types: IQ3_S, IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S, IQ1_M in this order (their grid tables are
  *                staged in shared memory)
  * < 0 on an unsupported type.
  * Reference: meta["max_rw"] and the NEW mask (gguf-plugin/gluon/tiles_grouped.py:181-202,1239-1265). */

@@ -3,7 +3,7 @@
  *
  * A plain-C restatement of the dequantisation arithmetic of the GGML block types the
  * quantized-linear method handles (Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ3_S,
- * IQ4_XS, and the codebook types IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S) and of the fp32 "dequantise, then
+ * IQ4_XS, and the codebook types IQ3_XXS, IQ2_XXS, IQ2_XS, IQ2_S, IQ1_M) and of the fp32 "dequantise, then
  * multiply" result they are checked against.  Nothing in
  * the shipped library links, loads or calls this file: only the tests, the smoke check and the
  * CPU-baseline leg of the benchmark use it, and only as the checker / the timed CPU figure.
@@ -37,7 +37,8 @@
 
 enum {
     T_Q4_0 = 2, T_Q5_0 = 6, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13,
-    T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ2_XS = 17, T_IQ3_XXS = 18, T_IQ4_NL = 20, T_IQ3_S = 21, T_IQ2_S = 22, T_IQ4_XS = 23
+    T_Q6_K = 14, T_IQ2_XXS = 16, T_IQ2_XS = 17, T_IQ3_XXS = 18, T_IQ4_NL = 20, T_IQ3_S = 21, T_IQ2_S = 22, T_IQ4_XS = 23,
+    T_IQ1_M = 29
 };
 
 static uint8_t g_iq3s_grid[512][4];   /* magnitudes, odd 1..15 */
@@ -45,6 +46,13 @@ static int8_t g_iq4_kvalues[16];
 static int g_tables_set = 0;
 static uint8_t g_iq3xxs_grid[256][4], g_iq2xxs_grid[256][8], g_iq2xs_grid[512][8], g_iq2s_grid[1024][8];
 static int g_iq_grids_set = 0;
+static int8_t g_iq1_grid[2048][8];     /* -1, 0, 1 */
+static int g_iq1_grid_set = 0;
+
+void oracle_set_iq1_grid(const int8_t *iq1_2048x8) {
+    memcpy(g_iq1_grid, iq1_2048x8, sizeof g_iq1_grid);
+    g_iq1_grid_set = 1;
+}
 
 void oracle_set_iq_grids(const uint8_t *iq3xxs_256x4, const uint8_t *iq2xxs_256x8, const uint8_t *iq2xs_512x8, const uint8_t *iq2s_1024x8) {
     memcpy(g_iq3xxs_grid, iq3xxs_256x4, sizeof g_iq3xxs_grid);
@@ -78,6 +86,7 @@ int oracle_bytes_per_256(int type) {
         case T_IQ2_XXS: return 66;
         case T_IQ2_XS: return 74;
         case T_IQ2_S: return 82;
+        case T_IQ1_M: return 56;
         default: return 0;
     }
 }
@@ -354,6 +363,28 @@ static void deq_iq2_s(const uint8_t *b, float *y) {
     }
 }
 
+/* IQ1_M: qs[32] low index bytes | qh[16]: per group of 8 a nibble (three high index bits, bit 3: the sign of delta) |
+ * scales[8] = four u16: bits 0..11 four 3-bit scales (one per 16 weights), bits 12..15 a nibble of the fp16 d.
+ * weight = d (2 s + 1) (g + delta), g in {-1, 0, 1}, delta = +-1/8 (gguf-py IQ1_M.dequantize_blocks; the reference has no kernel
+ * of its own for this type, it leaves it to the plugin's row path). */
+static void deq_iq1_m(const uint8_t *b, float *y) {
+    const uint8_t *qs = b, *qh = b + 32, *sc = b + 48;
+    uint16_t s16[4];
+    for (int i = 0; i < 4; i++) s16[i] = (uint16_t)(sc[2 * i] | (sc[2 * i + 1] << 8));
+    uint8_t dbits[2];
+    uint16_t dv = (uint16_t)((s16[0] >> 12) | ((s16[1] >> 8) & 0x00F0) | ((s16[2] >> 4) & 0x0F00) | (s16[3] & 0xF000));
+    dbits[0] = (uint8_t)(dv & 0xFF); dbits[1] = (uint8_t)(dv >> 8);
+    float d = f16_to_f32(dbits);
+    for (int g = 0; g < 32; g++) {
+        int nib = (qh[g >> 1] >> (4 * (g & 1))) & 0xF;
+        int idx = qs[g] | ((nib & 7) << 8);
+        int s = (s16[g >> 3] >> (3 * ((g >> 1) & 3))) & 7;
+        float dl = d * (float)(2 * s + 1);
+        float delta = (nib & 8) ? -0.125f : 0.125f;
+        for (int j = 0; j < 8; j++) y[8 * g + j] = dl * ((float)g_iq1_grid[idx][j] + delta);
+    }
+}
+
 /* one row segment of 256 weights -> 256 floats */
 static int deq_256(int type, const uint8_t *b, float *y) {
     switch (type) {
@@ -372,6 +403,7 @@ static int deq_256(int type, const uint8_t *b, float *y) {
         case T_IQ2_XXS: deq_iq2_xxs(b, y); return 0;
         case T_IQ2_XS: deq_iq2_xs(b, y); return 0;
         case T_IQ2_S: deq_iq2_s(b, y); return 0;
+        case T_IQ1_M: deq_iq1_m(b, y); return 0;
         default: return -1;
     }
 }
@@ -383,6 +415,7 @@ int oracle_dequantize(int type, const uint8_t *raw, int64_t n_rows, int64_t K, f
     if (K <= 0 || K % QK_K) return -2;
     if ((type == T_IQ3_S || type == T_IQ4_NL || type == T_IQ4_XS) && !g_tables_set) return -3;
     if ((type == T_IQ3_XXS || type == T_IQ2_XXS || type == T_IQ2_XS || type == T_IQ2_S) && !g_iq_grids_set) return -3;
+    if (type == T_IQ1_M && !g_iq1_grid_set) return -3;
     int64_t nb = K / QK_K;
 #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < n_rows; r++)
@@ -402,6 +435,7 @@ int oracle_matmul(int type, const uint8_t *raw, int64_t n_rows, int64_t K, const
     if (K <= 0 || K % QK_K) return -2;
     if ((type == T_IQ3_S || type == T_IQ4_NL || type == T_IQ4_XS) && !g_tables_set) return -3;
     if ((type == T_IQ3_XXS || type == T_IQ2_XXS || type == T_IQ2_XS || type == T_IQ2_S) && !g_iq_grids_set) return -3;
+    if (type == T_IQ1_M && !g_iq1_grid_set) return -3;
     int64_t nb = K / QK_K;
 #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < n_rows; r++) {

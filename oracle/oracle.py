@@ -25,7 +25,7 @@ _SO = os.path.join(_HERE, "libgguf_oracle.so")
 
 TYPES = {"Q4_0": 2, "Q5_0": 6, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14,
          "IQ4_NL": 20, "IQ3_S": 21, "IQ4_XS": 23}
-BYTES_PER_256 = {2: 144, 6: 176, 8: 272, 10: 84, 11: 110, 12: 144, 13: 176, 14: 210, 20: 144, 21: 110, 23: 136, 18: 98, 16: 66, 17: 74, 22: 82}
+BYTES_PER_256 = {2: 144, 6: 176, 8: 272, 10: 84, 11: 110, 12: 144, 13: 176, 14: 210, 20: 144, 21: 110, 23: 136, 18: 98, 16: 66, 17: 74, 22: 82, 29: 56}
 
 _lib = None
 
@@ -57,6 +57,14 @@ def iq_grids() -> list[np.ndarray]:
     return out
 
 
+def iq1_grid() -> np.ndarray:
+    """The 2048 x 8 entries (-1, 0, 1) of the IQ1 grid, from the gguf package."""
+    from gguf.quants import IQ1_M
+
+    IQ1_M.init_grid()
+    return np.ascontiguousarray(IQ1_M.grid.reshape(2048, 8).astype(np.int8))
+
+
 def iq4_kvalues() -> np.ndarray:
     from gguf.quants import IQ4_NL
 
@@ -78,6 +86,7 @@ def lib() -> ctypes.CDLL:
         g, kv = iq3s_grid_bytes(), iq4_kvalues()
         L.oracle_set_tables(g.ctypes.data_as(ctypes.c_void_p), kv.ctypes.data_as(ctypes.c_void_p))
         L.oracle_set_iq_grids(*[a.ctypes.data_as(ctypes.c_void_p) for a in iq_grids()])
+        L.oracle_set_iq1_grid(iq1_grid().ctypes.data_as(ctypes.c_void_p))
         _lib = L
     return _lib
 

@@ -286,11 +286,11 @@ def test_prefill_tcgen05_all_types(t):
         for m in (65, 128, 129, 257, 600):
             x = synth.activations(m, k, device=dev())
             wide = torch.full((m, n_out + 16), float("nan"), dtype=torch.bfloat16, device=dev())
-            ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out, out=wide[:, 8:8 + n_out])
+            ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out, out=wide[:, 8:8 + n_out], wtypes=[t])
             assert torch.isnan(wide[:, :8]).all() and torch.isnan(wide[:, 8 + n_out:]).all()
             y = wide[:, 8:8 + n_out]
             assert not torch.isnan(y).any()
-            assert torch.equal(y, ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out)), "not deterministic"
+            assert torch.equal(y, ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out, wtypes=[t])), "not deterministic"
             err = oracle.rel_err(y.float().cpu().numpy(), ref_gemm(x, raw, t))
             assert err < TOL_TIGHT, f"{F.TYPE_NAMES[t]} [{n_out}x{k}] M={m}: {err:.3e}"
 
@@ -313,7 +313,7 @@ def test_prefill_mixed_run_and_dispatch_boundary():
             col = 0
             for (n, t), tl in zip(parts, tiles):
                 d1 = torch.from_numpy(ops.build_descs([t], [n], k, 1)).to(dev())
-                assert torch.equal(y[:, col:col + n], ops.prefill_gemm(x, tl.reshape(-1), d1, n))
+                assert torch.equal(y[:, col:col + n], ops.prefill_gemm(x, tl.reshape(-1), d1, n, wtypes=[t]))
                 col += n
 
 
@@ -347,12 +347,12 @@ def test_prefill_full_size_down_projection_properties():
     tiles = ops.repack_tiles(raw, n_out, t)
     d1 = torch.from_numpy(ops.build_descs([t], [n_out], k, 1)).to(dev())
     x = synth.activations(m, k, device=dev())
-    y = ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out).float()
+    y = ops.prefill_gemm(x, tiles.reshape(-1), d1, n_out, wtypes=[t]).float()
     rows = torch.arange(0, n_out, 41, device=dev())
     cols_m = np.arange(0, m, 97)
     ref = ref_gemm(x[cols_m].cpu(), raw[rows].cpu(), t)
     assert oracle.rel_err(y[cols_m][:, rows].cpu().numpy(), ref) < TOL_TIGHT
-    y2 = ops.prefill_gemm((2 * x.float()).to(torch.bfloat16), tiles.reshape(-1), d1, n_out).float()
+    y2 = ops.prefill_gemm((2 * x.float()).to(torch.bfloat16), tiles.reshape(-1), d1, n_out, wtypes=[t]).float()
     assert float((y2 - 2 * y).abs().max()) <= 2 ** -7 * float(y.abs().max())
 
 

@@ -65,7 +65,7 @@ def test_encoders_are_reasonable():
     from hyperqwen_rtx4080s32_b200 import synth
 
     w = synth.gaussian_weights(16, 512, seed=1)
-    bound = {F.Q2_K: 0.45, F.Q3_K: 0.25, F.IQ3_S: 0.2, F.IQ3_XXS: 0.25, F.IQ2_XXS: 0.45, F.IQ2_XS: 0.4, F.IQ2_S: 0.36}
+    bound = {F.Q2_K: 0.45, F.Q3_K: 0.25, F.IQ3_S: 0.2, F.IQ3_XXS: 0.25, F.IQ2_XXS: 0.45, F.IQ2_XS: 0.4, F.IQ2_S: 0.36, F.IQ1_M: 0.55}
     for t in F.SUPPORTED_TYPES:
         wd = oracle.dequantize(synth.encode(w, t), t)
         assert np.sqrt(((wd - w) ** 2).mean()) / w.std() < bound.get(t, 0.12), F.TYPE_NAMES[t]
