@@ -19,7 +19,7 @@ import torch
 from . import formats as F
 from ._lib import DESC_WORDS, MAX_GEMV_ROWS, GqError, check, lib
 
-TILE_TYPES = F.SUPPORTED_TYPES   # every one of the eleven types is held tile-major (the reference: GLUON_TILE_TYPES)
+TILE_TYPES = F.SUPPORTED_TYPES   # every supported type is held tile-major (the reference: GLUON_TILE_TYPES)
 GEMV_MAX_ROWS = MAX_GEMV_ROWS    # the grouped kernel's own limit (the C ABI accepts up to 64 rows)
 DECODE_MAX_ROWS = 32             # row-count dispatch threshold: above it the tcgen05 kernel takes over
 
