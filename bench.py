@@ -218,6 +218,16 @@ def parity_before_timing(st, m, rank, world, dev):
     return errs
 
 
+# gguf-plugin/README.md:139-145: the reference's per-launch figures at 8 rows on its RTX 4080 SUPER, (microseconds, GB/s)
+REFERENCE_TABLE_M8 = {
+    (1024, 5120): {"Q3_K": (6.7, 335), "Q5_K": (8.9, 403), "Q6_K": (9.4, 458), "Q8_0": (11.2, 498), "Q4_K": (7.9, 373)},
+    (6144, 5120): {"Q3_K": (24.7, 546), "Q5_K": (36.7, 589), "Q6_K": (42.2, 612), "Q8_0": (52.1, 642), "Q4_K": (30.7, 577)},
+    (17408, 5120): {"Q3_K": (61.6, 622), "Q5_K": (94.8, 646), "Q6_K": (116.3, 629), "Q8_0": (148.3, 639), "Q4_K": (78.1, 642)},
+    (5120, 6144): {"Q3_K": (25.3, 534), "Q5_K": (35.8, 603), "Q6_K": (41.5, 623), "Q8_0": (52.0, 643), "Q4_K": (30.1, 587)},
+    (248320, 5120): {"Q3_K": (830.7, 658), "Q5_K": (1288.0, 679), "Q6_K": (1570.7, 664), "Q8_0": (1961.6, 689), "Q4_K": (1057.7, 676)},
+}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -466,6 +476,42 @@ def run_ours(args):
                                "dequantisation not counted in the flops; headline cell: Q4_K gate_up M = 2048",
                    "tflops": head["tflops"], "ms": head["ms"], "kernel": "gemm_prefill_kernel (tcgen05, TMEM accumulator)", "cells": cells}
 
+    # ---- the reference's own per-launch table (gguf-plugin/README.md:134-145: its shapes and types at 8 rows, CUDA-graph
+    # replays over copies of the layer exceeding the L2, GB/s of the raw block bytes), with its published RTX 4080 SUPER
+    # figures beside ours ----
+    type_table = None
+    if world == 1 and not args.no_type_table:
+        from hyperqwen_rtx4080s32_b200 import formats as F
+        from hyperqwen_rtx4080s32_b200 import synth
+
+        import numpy as _np
+
+        globals().update(np=_np, torch=torch)
+        type_table = {"what": "grouped kernel alone at M = 8, microseconds and GB/s of raw block bytes; ref = the reference's published figures on its "
+                              "RTX 4080 SUPER (736 GB/s) for the same shape and type", "cells": {}}
+        for (tn_out, tk), ref_row in REFERENCE_TABLE_M8.items():
+            for tname, (ref_us, ref_gbs) in ref_row.items():
+                wt = F.TYPE_IDS[tname]
+                nbytes = F.raw_bytes(wt, tn_out, tk)
+                ncopy = max(2, int(400e6 // nbytes))
+                packs = [ops.repack_tiles(synth.random_blocks(tn_out, tk, wt, seed=c, device=dev), tn_out, wt).reshape(-1) for c in range(ncopy)]
+                tx = synth.activations(m, tk, device=dev)
+                ts = ops.grouped_split_for(-(-tn_out // 64), tk // 256, m=m, block_bytes=F.BYTES_PER_256[wt])
+                td = torch.from_numpy(ops.build_descs([wt], [tn_out], tk, ts)).to(dev)
+                tws = torch.empty(_lib.lib().gq_workspace_bytes(m, tk, tn_out, ts), dtype=torch.uint8, device=dev)
+                ty = torch.empty((m, tn_out), dtype=torch.bfloat16, device=dev)
+                ops.grouped_gemm(tx, packs[0], td, ts, [wt], tn_out, out=ty, workspace=tws, phases=1)
+
+                def tfn():
+                    for pk_ in packs:
+                        ops.grouped_gemm(tx, pk_, td, ts, [wt], tn_out, out=ty, workspace=tws, phases=2)
+
+                us = 1e3 * _graph_time(tfn, ncopy)
+                type_table["cells"][f"{tname} {tn_out}x{tk}"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "split": ts,
+                                                                 "ref_us": ref_us, "ref_gbs": ref_gbs}
+                del packs, tx, td, tws, ty
+                torch.cuda.empty_cache()
+
     status = ops.device_status(dev)
     if world > 1:
         sflag = torch.tensor([status], device=dev)
@@ -515,6 +561,8 @@ def run_ours(args):
             line["other_batch_sizes"] = sweep
         if prefill is not None:
             line["prefill"] = prefill
+        if type_table is not None:
+            line["per_type_m8"] = type_table
         if world == 1 and not args.no_cpu:
             v, dt, info = cpu_sample(m, 2, target_s=12.0)
             line["cpu_baseline"] = dict(info, value=v, unit="GB/s")
@@ -773,6 +821,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill TFLOP/s leg")
+    ap.add_argument("--no-type-table", action="store_true", help="skip the reference's per-type table at its own shapes (M = 8)")
     ap.add_argument("--no-m-sweep", action="store_true", help="skip the other batch sizes of the config (M = 1, 4, 64; tensor parallel: 1, 64, 4096)")
     ap.add_argument("--unfused-allreduce", action="store_true", help="tensor parallel: all-reduce with the library's separate push kernel instead of inside the grouped kernel")
     ap.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: use NCCL for the row-parallel all-reduce instead of the library's push kernel")
