@@ -45,6 +45,8 @@ SIGNATURES = {
     "gq_fused_allreduce_buffer_bytes": (_i64, [_i32, _i64, _i64]),
     "gq_gemv_grouped_allreduce": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _i32, _i32, _vp,
                                          _i64, _i64, _vp]),
+    "gq_gemv_grouped_allreduce_silu_mul": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _i32, _vp, _i64, _i64, _vp, _i64, _i32, _i32, _vp,
+                                                  _i64, _i64, _vp]),
     "gq_prefill_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "gq_gemm_prefill": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _vp, _i64, _i64, _vp, _i64, _vp]),
     "gq_read_status": (_i32, [_vp, _i64, _vp]),

@@ -1659,10 +1659,10 @@ extern "C" int64_t gq_fused_allreduce_buffer_bytes(int world, int64_t max_m, int
     return fused_ar_header(max_n_total) + 2 * (int64_t)world * align256(max_m * max_n_total * 4);
 }
 
-extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
-                                         int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
-                                         void *workspace_dev, int64_t workspace_bytes, int rank, int world, const uint64_t *peer_buffers,
-                                         int64_t max_m, int64_t max_n_total, void *stream) {
+static int gemv_grouped_allreduce_impl(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                                       int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                                       void *workspace_dev, int64_t workspace_bytes, int rank, int world, const uint64_t *peer_buffers,
+                                       int64_t max_m, int64_t max_n_total, void *stream, const PreOp *pre) {
     if (world < 1 || world > GQ_AR_MAX_WORLD || rank < 0 || rank >= world || !peer_buffers) return GQ_ERR_ARG;
     if (max_m < 1 || max_m > GQ_MAX_GEMV_ROWS || M > max_m || n_total > max_n_total) return GQ_ERR_SHAPE;
     ArFused ar = {};
@@ -1692,7 +1692,29 @@ extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K
     }
     ar.counters = reinterpret_cast<uint32_t *>(peer_buffers[rank]);
     return gemv_grouped_impl(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
-                             workspace_bytes, stream, 7, nullptr, 0, &ar);
+                             workspace_bytes, stream, 7, nullptr, 0, &ar, pre);
+}
+
+extern "C" int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                                         int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                                         void *workspace_dev, int64_t workspace_bytes, int rank, int world, const uint64_t *peer_buffers,
+                                         int64_t max_m, int64_t max_n_total, void *stream) {
+    return gemv_grouped_allreduce_impl(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
+                                       workspace_bytes, rank, world, peer_buffers, max_m, max_n_total, stream, nullptr);
+}
+
+// the fused multiply + all-reduce of a row-parallel down_proj with silu_and_mul folded into its activation preparation:
+// x_dev is this rank's [M, 2K] slice pair (gate | up of its K columns, ldx >= 2K), 1..GQ_GEMV8_MAX_ROWS rows
+extern "C" int gq_gemv_grouped_allreduce_silu_mul(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev,
+                                                  const int32_t *desc_dev, int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy,
+                                                  int64_t n_total, void *workspace_dev, int64_t workspace_bytes, int rank, int world,
+                                                  const uint64_t *peer_buffers, int64_t max_m, int64_t max_n_total, void *stream) {
+    if (M < 0 || M > GQ_GEMV8_MAX_ROWS) return GQ_ERR_SHAPE;
+    if (ldx < 2 * K) return GQ_ERR_ARG;
+    PreOp po{};
+    po.kind = GQ_PRE_SILU_MUL; po.K = (int)K;
+    return gemv_grouped_allreduce_impl(x_dev, M, K, ldx, packed_dev, desc_dev, n_desc, split, run_info, y_dev, ldy, n_total, workspace_dev,
+                                       workspace_bytes, rank, world, peer_buffers, max_m, max_n_total, stream, &po);
 }
 
 // ---- small-message all-reduce over peer memory (tensor-parallel row-parallel layers) ---------------------

@@ -253,8 +253,8 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
         raise GqError(f"x must be bf16 [M, K], got {x.dtype} {tuple(x.shape)}")
     m, k = int(x.shape[0]), int(x.shape[1])
     if pre is not None:
-        if allreduce is not None or phases != 7 or m > PRE_MAX_ROWS:
-            raise GqError(f"a folded op needs the plain whole call and at most {PRE_MAX_ROWS} rows")
+        if phases != 7 or m > PRE_MAX_ROWS or (allreduce is not None and pre.kind != 1):
+            raise GqError(f"a folded op needs the whole call and at most {PRE_MAX_ROWS} rows (with the fused all-reduce: silu_and_mul only)")
         if pre.kind == 1:
             if k % 2:
                 raise GqError("silu_and_mul needs an even input width")
@@ -272,6 +272,14 @@ def grouped_gemm(x: torch.Tensor, packed: torch.Tensor, desc: torch.Tensor, spli
     L = lib()
     ws_bytes = check(L.gq_workspace_bytes(m, k, n_total, int(split)), "gq_workspace_bytes")
     ws = workspace if workspace is not None else torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    if pre is not None and allreduce is not None:
+        with torch.cuda.device(x.device):
+            check(L.gq_gemv_grouped_allreduce_silu_mul(x.data_ptr(), m, k, x.stride(0), packed.data_ptr(), desc.data_ptr(), int(desc.shape[0]),
+                                                       int(split), run_info(wtypes), out.data_ptr(), out.stride(0), n_total, ws.data_ptr(),
+                                                       ws.numel(), allreduce.rank, allreduce.world, allreduce.ptrs, allreduce.max_m,
+                                                       allreduce.max_n_total, _stream_ptr(x)), "gq_gemv_grouped_allreduce_silu_mul")
+        allreduce.used = True
+        return out
     if pre is not None:
         w = res = res_out = None
         if pre.kind == 2:
@@ -349,7 +357,11 @@ def mul_mat_tiles_grouped_pre(x: torch.Tensor, pre, packed: torch.Tensor, descs:
     s = grouped_split_for(n_tiles, nb, m=m, block_bytes=block_bytes, sms=sm_count(x.device))
     if s not in desc_splits:
         s = 1
-    return grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, pre=pre)
+    ar = _FUSED_AR
+    if ar is not None:
+        if pre.kind != 1 or not (m <= ar.max_m and n_total <= ar.max_n_total and s <= 8 and all(int(n) % 2 == 0 for n in n_outs)):
+            return mul_mat_tiles_grouped(pre.unfused(x), packed, descs, desc_splits, tiles, n_outs, weight_types, nb, block_bytes)
+    return grouped_gemm(x, packed, descs[desc_splits.index(s)], s, weight_types, n_total, pre=pre, allreduce=ar)
 
 
 def mul_mat_tiles_grouped(x: torch.Tensor, packed: torch.Tensor, descs: list[torch.Tensor], desc_splits: list[int],

@@ -208,6 +208,14 @@ int gq_gemv_grouped_allreduce(const void *x_dev, int64_t M, int64_t K, int64_t l
                               int64_t workspace_bytes, int rank, int world, const uint64_t *peer_buffers, int64_t max_m,
                               int64_t max_n_total, void *stream);
 
+/* gq_gemv_grouped_allreduce with silu_and_mul folded into the activation preparation (GQ_PRE_SILU_MUL of gq_gemv_grouped_pre): the
+ * row-parallel down_proj of a tensor-parallel decoder block in one call.  x_dev is this rank's [M, 2K] input, gate in columns 0..K-1
+ * and up in K..2K-1 of ITS K columns (ldx >= 2K); 1..16 rows.  Reference: none. */
+int gq_gemv_grouped_allreduce_silu_mul(const void *x_dev, int64_t M, int64_t K, int64_t ldx, const void *packed_dev, const int32_t *desc_dev,
+                                       int64_t n_desc, int split, int run_info, void *y_dev, int64_t ldy, int64_t n_total,
+                                       void *workspace_dev, int64_t workspace_bytes, int rank, int world, const uint64_t *peer_buffers,
+                                       int64_t max_m, int64_t max_n_total, void *stream);
+
 /* Workspace bytes of gq_gemm_prefill for a batch of M rows, a run of n_desc tiles and n_total output columns
  * (activations re-laid out for the tensor-core operand, row scales, status, and fp32 partial outputs when the call
  * will split K).  Depends on the current device's SM count. */

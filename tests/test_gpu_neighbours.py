@@ -128,3 +128,22 @@ def test_lm_head_shape_and_embedding_lookup(t):
     want = oracle.dequantize(raw[ids.reshape(-1)].cpu().numpy(), t).reshape(2, 3, k)
     assert np.array_equal(emb.cpu().numpy(), want)
     assert ops.device_status() == 0
+
+
+def test_silu_and_mul_folded_into_the_fused_all_reduce_call_single_rank():
+    """The row-parallel down_proj of a tensor-parallel block in one call (gq_gemv_grouped_allreduce_silu_mul), world size 1: bit-identical
+    to the folded call without the exchange; above 16 rows the op falls back to the unfused sequence."""
+    from hyperqwen_rtx4080s32_b200 import tp
+
+    k, n = 2048, 512
+    lin, raws = make_layer([n], k, F.Q4_K, 8500)
+    ctx = tp.LocalFusedAllReduce(max_m=64, max_n_total=n, device=dev())
+    for m in (1, 8, 16, 24):
+        gu = synth.activations(m, 2 * k, device=dev())
+        want = lin(gu, pre=ops.PreSiluMul())
+        with ops.fused_allreduce(ctx):
+            ctx.used = False
+            got = lin(gu, pre=ops.PreSiluMul())
+        assert torch.equal(got, want), m
+        assert ctx.used == (m <= 16) or m > 16
+    assert ops.device_status() == 0

@@ -134,6 +134,24 @@ def main() -> int:
     if not torch.equal(got, want):
         ok = False
         print(f"[rank {rank}] fused all-reduce: graph replay differs", flush=True)
+    # the row-parallel down projection with silu_and_mul folded into its preparation, summed over the ranks in the same call
+    lin_down = stk.layers[-1]["down"]
+    for m in (1, 8, 16):
+        up = stk.make_inputs(m)["down"]                                  # this rank's K columns (zero outside its own range)
+        gate = synth.activations(m, up.shape[1], seed=900 + m + rank, device=dev)
+        gu = torch.cat([gate, up], dim=1)
+        with ops.fused_allreduce(stk._far):
+            stk._far.used = False
+            want_y = lin_down(ops.PreSiluMul().unfused(gu)).clone()
+            stk._far.used = False
+            got_y = lin_down(gu, pre=ops.PreSiluMul()).clone()
+            folded_used = stk._far.used
+        torch.cuda.synchronize()
+        differ = (got_y != want_y).float().mean().item()
+        err = oracle.rel_err(got_y.float().cpu().numpy(), want_y.float().cpu().numpy())
+        if not folded_used or torch.isnan(got_y).any() or differ > 0.05 or err > 4e-3:
+            ok = False
+            print(f"[rank {rank}] folded silu_and_mul + fused all-reduce at M={m}: used {folded_used}, {differ:.4f} of the outputs differ, rel err {err:.3e}", flush=True)
     # a fused-exchange buffer is bound to the output width it was first used with
     lin_small = S.GGUFLinear(1024, [256])
     lin_small.load_shard(synth.random_blocks(256, 1024, F.Q4_K, seed=5).to(dev), F.Q4_K)
